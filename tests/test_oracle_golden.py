@@ -1,0 +1,69 @@
+"""Pins the CPU oracle (oracle/) against vectors produced by the reference's own
+torch code (tests/golden/make_golden.py) and against the hand-derived
+scheduler known answers."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention, quant, sched_meta
+from oracle.compare import check_close
+
+# The restatement is not op-for-op identical to the reference (fp32 summation order), so a bf16 output
+# may land on the neighbouring representable value: allow one bf16 ulp, and bound the whole tensor by cosine.
+BF16_ULP = 2.0 ** -7
+
+
+def _load(golden_dir, name):
+    return torch.load(os.path.join(golden_dir, name), weights_only=False)
+
+
+def test_sched_meta_known_answers(golden_dir):
+    cases = json.load(open(os.path.join(golden_dir, "sched_meta_known_answers.json")))["cases"]
+    for c in cases:
+        meta, ns = sched_meta.get_sched_meta(len(c["seqlens"]), c["num_sm_parts"], c["block_size_n"],
+                                             c["fixed_overhead"], seqlens_k=c["seqlens"])
+        assert meta[:, :7].tolist() == c["meta"]
+        assert ns.tolist() == c["num_splits"]
+
+
+def test_dense_decode_oracle_matches_reference(golden_dir):
+    for c in _load(golden_dir, "dense_decode.pt"):
+        out, lse = attention.dense_decode(c["q"], c["blocked_k"], c["block_table"], c["cache_seqlens"], c["d_v"], c["causal"])
+        assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
+        assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
+
+
+def test_quant_oracle_matches_reference(golden_dir):
+    c = _load(golden_dir, "quant_v32.pt")
+    qz = quant.quantize_v32(c["x"], pow2_scale=True)
+    assert qz.stride(0) == c["quant_stride0"]
+    assert torch.equal(qz.contiguous().view(torch.uint8), c["quant_bytes"])
+    dq = quant.dequantize_v32(c["quant_bytes"].view(torch.float8_e4m3fn))
+    assert torch.equal(dq.view(torch.int16), c["dequant"].view(torch.int16))
+    phys = quant.abs_to_physical_indices(c["abs_indices"], c["block_table"], 64)
+    assert torch.equal(phys, c["phys_indices"])
+
+
+def test_sparse_decode_oracle_matches_reference(golden_dir):
+    for c in _load(golden_dir, "sparse_decode.pt"):
+        kv = quant.dequantize_v32(c["kv_bytes"].view(torch.float8_e4m3fn))
+        extra = None
+        if "extra_kv_bytes" in c:
+            extra = quant.dequantize_v32(c["extra_kv_bytes"].view(torch.float8_e4m3fn))
+        out, lse = attention.sparse_decode(
+            c["q"], kv, c["indices"], c["sm_scale"], c["d_v"], c["attn_sink"], c["topk_length"],
+            extra, c.get("extra_indices"), c.get("extra_topk_length"))
+        assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
+        assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
+
+
+def test_sparse_prefill_oracle_matches_reference(golden_dir):
+    for c in _load(golden_dir, "sparse_prefill.pt"):
+        out, mx, lse = attention.sparse_prefill(c["q"], c["kv"], c["indices"], c["sm_scale"], c["d_v"],
+                                                c["attn_sink"], c["topk_length"], row_chunk=4)
+        assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
+        assert check_close("max_logits", mx, c["max_logits"], abs_tol=2e-6, rel_tol=1e-6)
+        assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
