@@ -1,0 +1,433 @@
+#!/usr/bin/env python
+"""Benchmark of the MLA decode / sparse-prefill path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One "step" is one pass of the public API call over one batch of synthetic input.  The default workload is
+dense BF16 MLA decode at the DeepSeek-V3 serving shape (batch 128 per GPU, h_q 128, mean sequence length
+4096, s_q 1); rank 0 prints ONE JSON line.  For N > 1 launch with torch.distributed.run: every rank runs its
+own batch on its own GPU (batch-sharded replicas, no collective on the data path), time is the maximum
+over ranks and `value` the aggregate over all GPUs.
+
+--impl reference times the CPU restatement of the reference's torch attention (oracle/) on the host cores
+on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D_QK, D_V = 576, 512
+
+
+# ------------------------------------------------------------------------------------------------------
+# workloads: inputs + algorithmic bytes / flops (conventions of the reference's own test scripts:
+# tests/test_flash_mla_dense_decoding.py:174-190, tests/lib.py:345-402)
+# ------------------------------------------------------------------------------------------------------
+def make_workload(name, device, seed):
+    from flashmla_b200 import workloads as W
+    if name in ("dense", "dense_sq2"):
+        s_q = 2 if name == "dense_sq2" else 1
+        b, h_q = 128, 128
+        seq = W.seqlens_normal(b, 4096, 512, 1, 8192, True, seed)
+        d = W.dense_decode_inputs(seq, s_q, h_q, 1, seed=seed, device=device, data_on_device=True)
+        S = int(seq.sum())
+        return dict(kind="dense", inputs=d, s_q=s_q, b=b, h_q=h_q, tokens=S,
+                    bytes=S * D_QK * 2 + b * s_q * h_q * D_QK * 2 + b * s_q * h_q * D_V * 2,
+                    flops=2.0 * h_q * s_q * S * (D_QK + D_V),
+                    desc=f"dense bf16 MLA decode b={b} h_q={h_q} h_kv=1 s_q={s_q} seqlens~N(4096,512^2) clip[1,8192] one=8192 causal paged(64)")
+    if name == "longctx":
+        b_total, h_q = 1024, 128
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        seq_all = W.seqlens_lognormal(b_total, 8192, 1.0, 256, 131072, seed=0)
+        per = b_total // world
+        seq = seq_all[rank * per:(rank + 1) * per].contiguous()
+        d = W.dense_decode_inputs(seq, 1, h_q, 1, seed=seed, device=device, data_on_device=True)
+        S = int(seq.sum())
+        return dict(kind="dense", inputs=d, s_q=1, b=per, h_q=h_q, tokens=S,
+                    bytes=S * D_QK * 2 + per * h_q * D_QK * 2 + per * h_q * D_V * 2,
+                    flops=2.0 * h_q * S * (D_QK + D_V),
+                    desc=f"dense bf16 MLA decode b={b_total} total (batch-sharded) h_q=128 s_q=1 seqlens lognormal(median 8192, sigma 1) clip[256,131072]")
+    if name == "sparse_decode":
+        b, h_q, s_kv, topk = 64, 128, 32768, 2048
+        d = W.sparse_decode_inputs(b, 1, h_q, s_kv, topk, seed=seed, device=device, data_on_device=True)
+        valid = b * d["n_valid"]
+        return dict(kind="sparse_decode", inputs=d, s_q=1, b=b, h_q=h_q, tokens=valid,
+                    bytes=valid * 656 + b * h_q * D_QK * 2 + b * h_q * D_V * 2,
+                    flops=2.0 * h_q * valid * (D_QK + D_V),
+                    desc=f"sparse fp8 MLA decode b={b} h_q={h_q} s_kv={s_kv} topk={topk} (5% padded -1) 656B records scale=amax/448")
+    if name == "sparse_prefill":
+        s_q, h_q, s_kv, topk = 4096, 128, 32768, 2048
+        d = W.sparse_prefill_inputs(s_q, h_q, s_kv, topk, causal_base=28672, seed=seed, device=device, data_on_device=True)
+        valid = s_q * topk
+        return dict(kind="sparse_prefill", inputs=d, s_q=s_q, b=1, h_q=h_q, tokens=valid,
+                    bytes=s_kv * D_QK * 2 + 4 * s_q * topk + s_q * h_q * (D_QK + D_V) * 2,
+                    flops=2.0 * valid * h_q * (D_QK + D_V),
+                    desc=f"token-sparse MLA prefill s_q={s_q} h_q={h_q} s_kv={s_kv} topk={topk} causal-valid indices")
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_step(w, sm_scale=D_QK ** -0.5, host=None):
+    """One pass through the public API.  With `host` (pinned host copies of the step's inputs) the inputs are
+    first copied to the device and the result is read back, all on the current stream."""
+    import flashmla_b200 as fm
+    d = w["inputs"]
+    if w["kind"] == "dense":
+        q, bt, sl = d["q"], d["block_table"], d["cache_seqlens"]
+        if host is not None:
+            q = host["q"].to(q.device, non_blocking=True)
+            bt = host["block_table"].to(q.device, non_blocking=True)
+            sl = host["cache_seqlens"].to(q.device, non_blocking=True)
+            meta, _ = fm.get_mla_metadata()          # the sequence lengths are new: the schedule is recomputed
+        else:
+            meta = w["meta"]
+        out, lse = fm.flash_mla_with_kvcache(q, d["blocked_k"], bt, sl, D_V, meta, None, sm_scale, True)
+    elif w["kind"] == "sparse_decode":
+        q, idx = d["q"], d["indices"]
+        if host is not None:
+            q = host["q"].to(q.device, non_blocking=True)
+            idx = host["indices"].to(q.device, non_blocking=True)
+        out, lse = fm.flash_mla_with_kvcache(q, d["kv_fp8"], None, None, D_V, w["meta"], None, sm_scale, False, True, idx)
+    else:
+        q, idx = d["q"], d["indices"]
+        if host is not None:
+            q = host["q"].to(q.device, non_blocking=True)
+            idx = host["indices"].to(q.device, non_blocking=True)
+        out, _, lse = fm.flash_mla_sparse_fwd(q, d["kv"], idx, sm_scale)
+    if host is not None:
+        host["out"].copy_(out, non_blocking=True)
+        host["lse"].copy_(lse, non_blocking=True)
+    return out, lse
+
+
+def make_host_buffers(w):
+    d = w["inputs"]
+    pin = lambda t: t.detach().cpu().contiguous().pin_memory()
+    host = {"q": pin(d["q"])}
+    if w["kind"] == "dense":
+        host["block_table"] = pin(d["block_table"])
+        host["cache_seqlens"] = pin(d["cache_seqlens"])
+    else:
+        host["indices"] = pin(d["indices"])
+    out, lse = run_step(w)
+    torch.cuda.synchronize()
+    host["out"] = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    host["lse"] = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for k, v in host.items() if k not in ("out", "lse"))
+    d2h = host["out"].numel() * host["out"].element_size() + host["lse"].numel() * host["lse"].element_size()
+    return host, h2d, d2h
+
+
+class KernelTimer:
+    """Records a CUDA event pair around every kernel launch of the API (on the launching stream)."""
+
+    def __init__(self):
+        self.pairs = {}
+        self._open = {}
+
+    def start(self, name):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self._open[name] = e
+
+    def stop(self, name):
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.pairs.setdefault(name, []).append((self._open.pop(name), e))
+
+    def mean_ms(self):
+        return {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in self.pairs.items()}
+
+    def launches(self):
+        return sum(len(v) for v in self.pairs.values())
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=float(p["hbm_gbs"]), tflops=float(p["bf16_tflops"]), tflops_sustained=float(p["bf16_tflops_sustained"]),
+                    source="measured")
+    return dict(hbm=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+# ------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle (port of the reference's torch attention) on the host cores, bounded sample
+# ------------------------------------------------------------------------------------------------------
+def cpu_baseline(w, budget_s=15.0):
+    from oracle import attention, quant
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    d = w["inputs"]
+    if w["kind"] == "dense":
+        b = w["b"]
+        order = [0] + list(range(1, b))
+        q, bk, bt, sl = d["q"].cpu(), None, d["block_table"].cpu(), d["cache_seqlens"].cpu()
+        done_tokens, t_used, n_req = 0, 0.0, 0
+        for i in order:
+            pages = bt[i, :(int(sl[i]) + 63) // 64].long()
+            kv_i = d["blocked_k"][pages.to(d["blocked_k"].device)].cpu()
+            bt_i = torch.arange(pages.numel(), dtype=torch.int32).view(1, -1)
+            t0 = time.perf_counter()
+            attention.dense_decode(q[i:i + 1], kv_i, bt_i, sl[i:i + 1], D_V, True)
+            t_used += time.perf_counter() - t0
+            done_tokens += int(sl[i])
+            n_req += 1
+            if t_used > budget_s:
+                break
+        frac = done_tokens / w["tokens"]
+        sample = f"{n_req} of {b} requests ({done_tokens} of {w['tokens']} KV tokens), oracle.attention.dense_decode"
+    elif w["kind"] == "sparse_decode":
+        b = w["b"]
+        t_used, n_req = 0.0, 0
+        for i in range(b):
+            idx = d["indices"][i:i + 1].cpu()
+            pages = torch.unique(idx[idx >= 0] // 64)
+            remap = torch.full((d["kv_fp8"].size(0),), -1, dtype=torch.int64)
+            remap[pages.long()] = torch.arange(pages.numel())
+            kv_raw = d["kv_fp8"][pages.to(d["kv_fp8"].device).long()].cpu().contiguous()
+            idx_s = torch.where(idx >= 0, (remap[(idx.clamp_min(0) // 64).long()] * 64 + idx % 64).to(torch.int32), idx)
+            qi = d["q"][i:i + 1].cpu()
+            t0 = time.perf_counter()
+            kv_deq = quant.dequantize_v32(kv_raw)
+            attention.sparse_decode(qi, kv_deq, idx_s, D_QK ** -0.5, D_V)
+            t_used += time.perf_counter() - t0
+            n_req += 1
+            if t_used > budget_s:
+                break
+        frac = n_req / b
+        sample = f"{n_req} of {b} requests, oracle.quant.dequantize_v32 (touched pages) + oracle.attention.sparse_decode"
+    else:
+        rows = 0
+        t_used = 0.0
+        q, kv, idx = d["q"], d["kv"].cpu(), d["indices"]
+        while t_used < budget_s and rows < w["s_q"]:
+            r1 = min(rows + 16, w["s_q"])
+            qi, ii = q[rows:r1].cpu(), idx[rows:r1].cpu()
+            t0 = time.perf_counter()
+            attention.sparse_prefill(qi, kv, ii, D_QK ** -0.5, D_V, row_chunk=16)
+            t_used += time.perf_counter() - t0
+            rows = r1
+        frac = rows / w["s_q"]
+        sample = f"{rows} of {w['s_q']} query rows, oracle.attention.sparse_prefill"
+    return dict(seconds=t_used, frac=frac, cores=cores, sample=sample)
+
+
+def metric_of(w):
+    if w["kind"] == "sparse_prefill":
+        return "mla_sparse_prefill_tflops", "TFLOP/s", w["flops"] / 1e12
+    if w["kind"] == "sparse_decode":
+        return "mla_sparse_decode_tflops", "TFLOP/s", w["flops"] / 1e12
+    return "mla_dense_decode_hbm_gbs", "GB/s", w["bytes"] / 1e9
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill"])
+    ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+        w = make_workload(args.workload, dev, seed=0)
+        metric, unit, units_per_step = metric_of(w)
+        # each "step" is one bounded sample of the workload on all host cores
+        vals = []
+        for i in range(args.warmup + args.steps):
+            r = cpu_baseline(w, budget_s=6.0)
+            if i >= args.warmup:
+                vals.append(units_per_step * r["frac"] / r["seconds"])
+        v = sum(vals) / len(vals)
+        line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": 1e3 * units_per_step / v, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": w["desc"], "note": "CPU port of the reference's torch attention (oracle/), bounded sample, extrapolated to a full step"},
+                "cpu_baseline": {"value": v, "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import flashmla_b200 as fm
+    from flashmla_b200 import flash_mla_interface as fmi
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    fm.set_impl(args.kernel)
+
+    w = make_workload(args.workload, dev, seed=rank)
+    w["meta"] = fm.get_mla_metadata()[0]
+    metric, unit, units_per_step = metric_of(w)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ------------------------------------------------------------------------
+    for _ in range(args.warmup):
+        run_step(w)
+    timer = KernelTimer()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        fmi.set_kernel_timer(timer)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            run_step(w)
+        e1.record()
+        barrier()
+        fmi.set_kernel_timer(None)
+    ms_total = e0.elapsed_time(e1)
+    kernel_ms = timer.mean_ms()
+    launches = timer.launches()
+
+    # ---- end-to-end timing: host buffers in, result out --------------------------------------------------
+    host, h2d, d2h = make_host_buffers(w)
+    for _ in range(2):
+        run_step(w, host=host)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        run_step(w, host=host)
+    f1.record()
+    barrier()
+    ms_e2e_total = f0.elapsed_time(f1)
+
+    # ---- reduce over ranks ---------------------------------------------------------------------------------
+    stats = torch.tensor([ms_total, ms_e2e_total, units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"])],
+                         dtype=torch.float64, device=dev)
+    if dist is not None:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms_total, ms_e2e_total = float(mx[0]), float(mx[1])
+        units_all, tokens_all, flops_all, bytes_all = float(sm[2]), float(sm[3]), float(sm[4]), float(sm[5])
+    else:
+        units_all, tokens_all, flops_all, bytes_all = units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"])
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / args.steps
+    ms_e2e = ms_e2e_total / args.steps
+    peaks = measured_peaks()
+    main_kernel = {"dense": "mla_dense_decode_fwd", "sparse_decode": "mla_sparse_decode_fwd",
+                   "sparse_prefill": "mla_sparse_prefill_fwd"}[w["kind"]]
+    k_ms = kernel_ms[main_kernel]
+    if w["kind"] == "dense":
+        roof = {"bound": "hbm", "achieved": w["bytes"] / 1e9 / (k_ms / 1e3), "peak": peaks["hbm"], "unit": "GB/s"}
+    else:
+        roof = {"bound": "tensor", "achieved": w["flops"] / 1e12 / (k_ms / 1e3), "peak": peaks["tflops"], "unit": "TFLOP/s"}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["traffic"] = None
+    roof["kernel"] = main_kernel
+    roof["kernel_ms"] = k_ms
+    roof["peak_source"] = peaks["source"]
+
+    line = {
+        "metric": metric, "value": units_all / (ms_step / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": "inputs larger than L2 (KV cache streamed once per step)",
+                   "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel]},
+        "tflops": flops_all / 1e12 / (ms_step / 1e3), "hbm_gbs": bytes_all / 1e9 / (ms_step / 1e3),
+        "kv_tokens_per_s": tokens_all / (ms_step / 1e3),
+        "kernel_ms": kernel_ms, "gpu_launches": launches,
+        "roofline": roof, "clocks": clocks.summary(),
+        "e2e": {"value": units_all / (ms_e2e / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e},
+    }
+    if not args.no_cpu_baseline and world >= 1:
+        r = cpu_baseline(w, budget_s=12.0)
+        line["cpu_baseline"] = {"value": units_per_step * r["frac"] / r["seconds"], "unit": unit, "cores": r["cores"],
+                                "kind": "port", "sample": r["sample"]}
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

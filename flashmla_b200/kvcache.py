@@ -1,0 +1,34 @@
+"""FP8 KV-cache records for the sparse decode path (the cache-write side of the path).
+
+Per token 656 bytes: 512 float8_e4m3fn "NoPE" values quantised per group of 128 with one fp32
+scale per group (x ~= fp8 * scale), the 4 scales, then 64 bf16 "RoPE" values stored as they are
+(layout: flash_mla/flash_mla_interface.py:92-98 of the reference).  Runs on whatever device the
+input lives on; it is a utility for producing caches, not part of the decode hot path.
+"""
+import torch
+
+D_QK, D_NOPE, D_ROPE, GROUP, NUM_GROUPS = 576, 512, 64, 128, 4
+BYTES_PER_TOKEN = D_NOPE + 4 * NUM_GROUPS + 2 * D_ROPE
+
+
+def quantize_fp8_kvcache(blocked_k: torch.Tensor, pow2_scale: bool = False, pad_rows: int = 0) -> torch.Tensor:
+    """blocked_k [num_blocks, block_size, 1, 576] bf16 -> [num_blocks, block_size, 1, 656] float8_e4m3fn.
+
+    scale = amax/448 of each 128-value group; with pow2_scale it is rounded up to a power of two
+    (the convention of the reference's test quantiser).  pad_rows > 0 leaves spare rows at the end of
+    every block, which makes the block stride differ from block_size * 656."""
+    nb, bs, h_k, d = blocked_k.shape
+    assert h_k == 1 and d == D_QK
+    x = blocked_k.squeeze(2)
+    buf = torch.empty((nb, bs + pad_rows, BYTES_PER_TOKEN), dtype=torch.float8_e4m3fn, device=blocked_k.device)
+    res = buf[:, :bs, :]
+    grp = x[..., :D_NOPE].reshape(nb, bs, NUM_GROUPS, GROUP).float()
+    scale = grp.abs().amax(dim=-1) / 448.0
+    if pow2_scale:
+        scale = torch.pow(2, torch.clamp_min(scale, 1e-4).log2().ceil())
+    else:
+        scale = torch.clamp_min(scale, 1e-30)
+    res[..., :D_NOPE] = (grp / scale.unsqueeze(-1)).reshape(nb, bs, D_NOPE).to(torch.float8_e4m3fn)
+    res[..., D_NOPE:D_NOPE + 4 * NUM_GROUPS].view(torch.float32)[:] = scale
+    res[..., D_NOPE + 4 * NUM_GROUPS:].view(torch.bfloat16)[:] = x[..., D_NOPE:]
+    return res.view(nb, bs, 1, BYTES_PER_TOKEN)

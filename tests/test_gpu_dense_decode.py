@@ -1,0 +1,92 @@
+"""GPU parity of dense BF16 MLA decode against the CPU oracle, through the public API
+(which calls the C ABI)."""
+import os
+
+import pytest
+import torch
+
+from oracle import attention
+from tests.helpers import assert_lse_close, assert_out_close, non_contiguousify
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(q, blocked_k, block_table, cache_seqlens, d_v, causal, impl=0):
+    import flashmla_b200 as fm
+    fm.set_impl(impl)
+    try:
+        meta, _ = fm.get_mla_metadata()
+        out, lse = fm.flash_mla_with_kvcache(q, blocked_k, block_table, cache_seqlens, d_v, meta, None, causal=causal)
+        # second call re-uses the cached scheduler metadata
+        out2, lse2 = fm.flash_mla_with_kvcache(q, blocked_k, block_table, cache_seqlens, d_v, meta, None, causal=causal)
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    finally:
+        fm.set_impl(0)
+    return out, lse
+
+
+def test_golden_fixtures(golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "dense_decode.pt"), weights_only=False):
+        out, lse = _run(c["q"].to(DEV), c["blocked_k"].to(DEV), c["block_table"].to(DEV), c["cache_seqlens"].to(DEV),
+                        c["d_v"], c["causal"])
+        assert_out_close("out", out, c["out"])
+        assert_lse_close("lse", lse, c["lse"])
+
+
+def _case(b, s_q, h_q, h_kv, seqlens, causal, seed, noncontig=False, impl=0):
+    from flashmla_b200 import workloads as W
+    seq = torch.tensor(seqlens, dtype=torch.int32)
+    d = W.dense_decode_inputs(seq, s_q, h_q, h_kv, seed=seed, device="cpu", poison_unused=True)
+    ref_out, ref_lse = attention.dense_decode(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], 512, causal)
+    q, k, bt = d["q"].to(DEV), d["blocked_k"].to(DEV), d["block_table"].to(DEV)
+    if noncontig:
+        q, k, bt = non_contiguousify(q), non_contiguousify(k), non_contiguousify(bt)
+    out, lse = _run(q, k, bt, d["cache_seqlens"].to(DEV), 512, causal, impl)
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+
+
+def test_config1_tiny():
+    """batch 4, s_q 1, h_q 16, seqlens uniform in [64, 512], causal, softmax_scale 576^-0.5."""
+    g = torch.Generator().manual_seed(0)
+    seq = torch.randint(64, 513, (4,), generator=g).tolist()
+    _case(4, 1, 16, 1, seq, True, seed=0)
+
+
+@pytest.mark.parametrize("s_q,h_q,h_kv,causal", [
+    (1, 128, 1, False), (2, 128, 1, True), (1, 64, 1, False), (4, 9, 1, True), (2, 126, 2, True), (1, 3, 3, False),
+    (2, 63, 1, True), (1, 1, 1, False),
+])
+def test_shape_grid(s_q, h_q, h_kv, causal):
+    seqlens = [140, 4096 // 8 + 3, 20, 0, 64, 1, 1000, 65]
+    _case(len(seqlens), s_q, h_q, h_kv, seqlens, causal, seed=s_q * 1000 + h_q, noncontig=(h_q % 2 == 1))
+
+
+def test_many_splits_long_sequence():
+    """One long request next to short ones: the long one is split over many SM partitions."""
+    _case(3, 1, 128, 1, [20000, 64, 300], False, seed=5)
+
+
+def test_serving_shape_sample():
+    """Serving shape (batch 128, h_q 128, seqlens ~ N(4096, 512^2) clipped to [1, 8192], one forced to 8192,
+    causal, s_q in {1, 2}): the full batch runs on the GPU, a sample of requests is checked against the oracle."""
+    from flashmla_b200 import workloads as W
+    import flashmla_b200 as fm
+    seq = W.seqlens_normal(128, 4096, 512, 1, 8192, True, seed=0)
+    for s_q in (1, 2):
+        d = W.dense_decode_inputs(seq, s_q, 128, 1, seed=7, device="cpu")
+        meta, _ = fm.get_mla_metadata()
+        out, lse = fm.flash_mla_with_kvcache(d["q"].to(DEV), d["blocked_k"].to(DEV), d["block_table"].to(DEV),
+                                             d["cache_seqlens"].to(DEV), 512, meta, None, causal=True)
+        torch.cuda.synchronize()
+        sample = [0, 1, 17, 63, 127]
+        ref_out, ref_lse = attention.dense_decode(d["q"][sample], d["blocked_k"], d["block_table"][sample],
+                                                  d["cache_seqlens"][sample], 512, True)
+        assert_out_close("out", out[sample], ref_out)
+        assert_lse_close("lse", lse[sample], ref_lse)
+        # size-independent properties over the whole batch: finite results, and since a softmax output is a
+        # convex combination of value rows, |out| is bounded by the largest |value| of the cache
+        assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+        assert out.float().abs().max() <= d["blocked_k"].float().abs().max()

@@ -1,0 +1,144 @@
+"""GPU parity of sparse FP8 decode and token-sparse prefill against the CPU oracle, through the public API."""
+import os
+
+import pytest
+import torch
+
+from oracle import attention, quant
+from tests.helpers import assert_lse_close, assert_out_close, non_contiguousify
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _dev(t):
+    return None if t is None else t.to(DEV)
+
+
+def _decode(q, kv, indices, sm_scale, attn_sink=None, topk_length=None, extra_kv=None, extra_indices=None,
+            extra_topk_length=None):
+    import flashmla_b200 as fm
+    meta, _ = fm.get_mla_metadata()
+    out, lse = fm.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, sm_scale, False, True, indices, attn_sink,
+                                         extra_kv, extra_indices, topk_length, extra_topk_length)
+    torch.cuda.synchronize()
+    return out, lse
+
+
+def test_sparse_decode_golden(golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "sparse_decode.pt"), weights_only=False):
+        kv = c["kv_bytes"].view(torch.float8_e4m3fn)
+        out, lse = _decode(_dev(c["q"]), _dev(kv), _dev(c["indices"]), c["sm_scale"], _dev(c["attn_sink"]),
+                           _dev(c["topk_length"]),
+                           _dev(c["extra_kv_bytes"].view(torch.float8_e4m3fn)) if "extra_kv_bytes" in c else None,
+                           _dev(c.get("extra_indices")), _dev(c.get("extra_topk_length")))
+        assert_out_close("out", out, c["out"])
+        assert_lse_close("lse", lse, c["lse"])
+
+
+@pytest.mark.parametrize("b,s_q,h_q,s_kv,topk,pow2,sink", [
+    (4, 1, 128, 1024, 256, False, False),
+    (3, 2, 128, 2048, 512, True, True),
+    (5, 1, 64, 512, 128, False, True),
+    (2, 3, 16, 640, 192, False, False),
+])
+def test_sparse_decode_cases(b, s_q, h_q, s_kv, topk, pow2, sink):
+    from flashmla_b200 import workloads as W
+    d = W.sparse_decode_inputs(b, s_q, h_q, s_kv, topk, seed=b * 10 + s_q, device="cpu", pow2_scale=pow2, pad_rows=1)
+    assert d["kv_fp8"].stride(0) == 65 * 656
+    kv_deq = quant.dequantize_v32(d["kv_fp8"])
+    # the reference's habit: every token no index refers to is NaN in the checker's cache
+    attn_sink = None
+    if sink:
+        attn_sink = torch.randn(h_q, generator=torch.Generator().manual_seed(1))
+        attn_sink[0] = float("inf")
+        attn_sink[-1] = float("-inf")
+    topk_length = torch.randint(0, topk + 1, (b,), generator=torch.Generator().manual_seed(2), dtype=torch.int32) if sink else None
+    ref_out, ref_lse = attention.sparse_decode(d["q"], kv_deq, d["indices"], 576 ** -0.5, 512, attn_sink, topk_length)
+    idx = non_contiguousify(d["indices"].to(DEV))
+    out, lse = _decode(non_contiguousify(d["q"].to(DEV)), d["kv_fp8"].to(DEV), idx, 576 ** -0.5, _dev(attn_sink), _dev(topk_length))
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+
+
+def test_sparse_decode_all_invalid_and_unused_nan():
+    """A request whose indices are all -1 gives out = 0 and lse = +inf; cache rows that no index refers to may
+    hold NaN bytes without leaking into the result."""
+    from flashmla_b200 import workloads as W
+    d = W.sparse_decode_inputs(3, 1, 128, 512, 128, seed=3, device="cpu")
+    d["indices"][1] = -1
+    kv = d["kv_fp8"].clone()
+    used = torch.zeros(kv.size(0) * 64, dtype=torch.bool)
+    used[d["indices"][d["indices"] >= 0].long()] = True
+    raw = kv.view(torch.uint8).view(-1, 656)
+    raw[~used] = 0x7F                      # e4m3 NaN pattern, and NaN-ish scale / RoPE bytes
+    kv_deq = quant.dequantize_v32(kv)
+    ref_out, ref_lse = attention.sparse_decode(d["q"], kv_deq, d["indices"], 576 ** -0.5, 512)
+    out, lse = _decode(d["q"].to(DEV), kv.to(DEV), d["indices"].to(DEV), 576 ** -0.5)
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+    assert (out[1] == 0).all() and (lse[1] == float("inf")).all()
+
+
+def test_sparse_decode_config3_sample():
+    """batch 64, h_q 128, 32768 tokens per sequence, topk 2048 with the last 5% of each row -1, scale = amax/448:
+    the whole batch runs on the GPU, a sample of requests is checked against the oracle."""
+    from flashmla_b200 import workloads as W
+    d = W.sparse_decode_inputs(64, 1, 128, 32768, 2048, seed=0, device=DEV, data_on_device=True)
+    out, lse = _decode(d["q"], d["kv_fp8"], d["indices"], 576 ** -0.5)
+    sample = [0, 31, 63]
+    idx = d["indices"][sample].cpu()
+    # de-quantise only the pages the sample touches (the oracle works on a compacted cache)
+    pages = torch.unique(idx[idx >= 0] // 64)
+    remap = torch.full((d["kv_fp8"].size(0),), -1, dtype=torch.int64)
+    remap[pages.long()] = torch.arange(pages.numel())
+    kv_small = quant.dequantize_v32(d["kv_fp8"][pages.to(DEV).long()].cpu().contiguous())
+    idx_small = torch.where(idx >= 0, (remap[(idx.clamp_min(0) // 64).long()] * 64 + idx % 64).to(torch.int32), idx)
+    ref_out, ref_lse = attention.sparse_decode(d["q"][sample].cpu(), kv_small, idx_small, 576 ** -0.5, 512)
+    assert_out_close("out", out[sample], ref_out)
+    assert_lse_close("lse", lse[sample], ref_lse)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+
+
+def _prefill(q, kv, indices, sm_scale, attn_sink=None, topk_length=None):
+    import flashmla_b200 as fm
+    out, mx, lse = fm.flash_mla_sparse_fwd(q, kv, indices, sm_scale, 512, attn_sink, topk_length)
+    torch.cuda.synchronize()
+    return out, mx, lse
+
+
+def test_sparse_prefill_golden(golden_dir):
+    for c in torch.load(os.path.join(golden_dir, "sparse_prefill.pt"), weights_only=False):
+        out, mx, lse = _prefill(_dev(c["q"]), _dev(c["kv"]), _dev(c["indices"]), c["sm_scale"], _dev(c["attn_sink"]),
+                                _dev(c["topk_length"]))
+        assert_out_close("out", out, c["out"])
+        assert_lse_close("max_logits", mx, c["max_logits"])
+        assert_lse_close("lse", lse, c["lse"])
+
+
+@pytest.mark.parametrize("s_q,h_q,s_kv,topk", [(62, 128, 2000, 256), (7, 64, 300, 128), (33, 128, 128, 384)])
+def test_sparse_prefill_cases(s_q, h_q, s_kv, topk):
+    from flashmla_b200 import workloads as W
+    d = W.sparse_prefill_inputs(s_q, h_q, s_kv, topk, seed=s_q, device="cpu")
+    zoo = torch.tensor([-2147483648, -123456, -1, s_kv, 114514, 1919810, 2147480000, 2147483647], dtype=torch.int32)
+    idx = d["indices"]
+    idx[idx < 0] = zoo[torch.arange(int((idx < 0).sum())) % zoo.numel()]
+    idx[::5, 0, 3] = s_kv
+    ref = attention.sparse_prefill(d["q"], d["kv"], idx, 0.5 * 576 ** -0.5, 512)
+    out, mx, lse = _prefill(non_contiguousify(d["q"].to(DEV)), non_contiguousify(d["kv"].to(DEV)),
+                            non_contiguousify(idx.to(DEV)), 0.5 * 576 ** -0.5)
+    assert_out_close("out", out, ref[0])
+    assert_lse_close("max_logits", mx, ref[1])
+    assert_lse_close("lse", lse, ref[2])
+
+
+def test_sparse_prefill_config4_rows():
+    """s_kv 32768, topk 2048, h_q 128, causal-valid indices (query t draws from [0, 28672 + t]): a slice of query
+    rows at the full KV size is checked against the oracle."""
+    from flashmla_b200 import workloads as W
+    d = W.sparse_prefill_inputs(48, 128, 32768, 2048, causal_base=28672, seed=0, device="cpu")
+    ref = attention.sparse_prefill(d["q"], d["kv"], d["indices"], 576 ** -0.5, 512, row_chunk=8)
+    out, mx, lse = _prefill(d["q"].to(DEV), d["kv"].to(DEV), d["indices"].to(DEV), 576 ** -0.5)
+    assert_out_close("out", out, ref[0])
+    assert_lse_close("max_logits", mx, ref[1])
+    assert_lse_close("lse", lse, ref[2])
