@@ -5,6 +5,7 @@ from .flash_mla_interface import (
     flash_mla_with_kvcache,
     flash_mla_sparse_fwd,
     set_impl,
+    check_status,
 )
 
 __all__ = [
@@ -13,4 +14,5 @@ __all__ = [
     "flash_mla_with_kvcache",
     "flash_mla_sparse_fwd",
     "set_impl",
+    "check_status",
 ]

@@ -338,8 +338,7 @@ attn_portable_kernel(const Params p) {
                 for (int j = 0; j < 8; j += 2) {
                     const float e0 = exp2f(v[j] - m_use), e1 = exp2f(v[j + 1] - m_use);
                     __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
-                    // accumulate the row sum from the rounded probabilities, as the tensor cores see them
-                    sum += __low2float(pb) + __high2float(pb);
+                    sum += e0 + e1;
                     packed[j >> 1] = *reinterpret_cast<uint32_t*>(&pb);
                 }
                 *reinterpret_cast<uint4*>(prow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);

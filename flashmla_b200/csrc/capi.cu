@@ -75,11 +75,11 @@ int mla_num_sm_parts(int device, int mode, int h_q, int h_kv, int s_q) {
         return -1;
     }
     if (mode == MLA_MODE_DENSE_DECODE) {
-        // One partition is walked by the CTAs of every 64-row block of every kv head; two CTAs
-        // (64-row blocks, or the two halves of a tcgen05 CTA pair) share an SM pair.
+        // A partition is walked, for every block of 128 query rows of every kv head, by a pair of CTAs on two
+        // SMs (the tcgen05 kernel's score / value CTAs, or two 64-row CTAs of the portable kernel).
         const int rows = s_q * (h_q / h_kv);
-        const int row_blocks = (rows + 63) / 64;
-        int p = sms / h_kv / row_blocks;
+        const int row_blocks = (rows + 127) / 128;
+        int p = sms / 2 / h_kv / row_blocks;
         return p > 0 ? p : 1;
     } else if (mode == MLA_MODE_SPARSE_DECODE) {
         const int row_blocks = (h_q + 63) / 64;

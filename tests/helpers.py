@@ -8,9 +8,12 @@ from oracle.compare import check_close, cos_diff, max_abs_err
 OUT_COS_TOL = 1e-5
 OUT_ABS_TOL = 2e-2
 LSE_TOL = 1e-3
-# The reference's own (tighter) test tolerances (tests/test_flash_mla_dense_decoding.py:170-171,
-# tests/test_flash_mla_sparse_decoding.py:228-229, tests/test_flash_mla_sparse_prefill.py:46-48).
-REF_OUT = dict(abs_tol=1e-3, rel_tol=2.01 / 128, cos_diff_tol=7e-6)
+# The reference's own test tolerances (tests/test_flash_mla_dense_decoding.py:170-171,
+# tests/test_flash_mla_sparse_decoding.py:228-229, tests/test_flash_mla_sparse_prefill.py:46-48): out passes
+# element-wise on abs 8e-4..1e-3 OR rel 2.01/128, plus a cosine bound.  Its absolute bound is sized for its
+# test data (randn/10, values of std 0.1); the inputs here are N(0,1) as the benchmark configurations ask,
+# ten times larger, so the absolute bound scales by ten.  The relative and cosine bounds are scale-free.
+REF_OUT = dict(abs_tol=1e-2, rel_tol=2.01 / 128, cos_diff_tol=7e-6)
 REF_LSE = dict(abs_tol=1e-5, rel_tol=8.01 / 65536)
 
 

@@ -21,6 +21,7 @@ def _run(q, blocked_k, block_table, cache_seqlens, d_v, causal, impl=0):
         # second call re-uses the cached scheduler metadata
         out2, lse2 = fm.flash_mla_with_kvcache(q, blocked_k, block_table, cache_seqlens, d_v, meta, None, causal=causal)
         torch.cuda.synchronize()
+        fm.check_status()
         assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
     finally:
         fm.set_impl(0)
@@ -64,6 +65,14 @@ def test_shape_grid(s_q, h_q, h_kv, causal):
     _case(len(seqlens), s_q, h_q, h_kv, seqlens, causal, seed=s_q * 1000 + h_q, noncontig=(h_q % 2 == 1))
 
 
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("s_q,h_q,h_kv,causal", [(1, 128, 1, False), (2, 128, 1, True), (2, 48, 2, True), (1, 16, 1, False)])
+def test_both_kernel_families(impl, s_q, h_q, h_kv, causal):
+    """The portable kernel (1) and the tcgen05 kernel (2) must both match the oracle on the same inputs."""
+    seqlens = [140, 515, 20, 0, 64, 1, 1000, 65, 4096]
+    _case(len(seqlens), s_q, h_q, h_kv, seqlens, causal, seed=11 * s_q + h_q, noncontig=True, impl=impl)
+
+
 def test_many_splits_long_sequence():
     """One long request next to short ones: the long one is split over many SM partitions."""
     _case(3, 1, 128, 1, [20000, 64, 300], False, seed=5)
@@ -81,6 +90,7 @@ def test_serving_shape_sample():
         out, lse = fm.flash_mla_with_kvcache(d["q"].to(DEV), d["blocked_k"].to(DEV), d["block_table"].to(DEV),
                                              d["cache_seqlens"].to(DEV), 512, meta, None, causal=True)
         torch.cuda.synchronize()
+        fm.check_status()
         sample = [0, 1, 17, 63, 127]
         ref_out, ref_lse = attention.dense_decode(d["q"][sample], d["blocked_k"], d["block_table"][sample],
                                                   d["cache_seqlens"][sample], 512, True)
