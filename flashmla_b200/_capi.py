@@ -9,7 +9,7 @@ import threading
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libflashmla_b200.so")
+LIB_PATH = os.environ.get("FLASHMLA_B200_LIB") or os.path.join(_HERE, "libflashmla_b200.so")
 
 MLA_MODE_DENSE_DECODE = 0
 MLA_MODE_SPARSE_DECODE = 1

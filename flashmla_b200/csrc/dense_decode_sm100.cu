@@ -4,16 +4,20 @@
 // Problem shape per (request, kv head): 128 query rows (query token x head, padded with zero rows)
 // against a paged stream of 576-wide K rows whose first 512 columns are also V.  The fp32 output
 // accumulator O[128 x 512] fills all 512 columns of one SM's tensor memory, so the work of one row
-// block is split over a CLUSTER OF TWO CTAs on two SMs that walk the same KV range:
+// block is split over a CLUSTER OF TWO CTAs on two SMs that walk the same KV range in tiles of 128
+// tokens (two pages):
 //
-//   CTA 0 ("score" CTA)   TMEM: Q as the A operand (288 columns of packed bf16) + two S buffers.
-//                         S = Q K^T per 64-token page (36 MMAs 128x64x16, A from tensor memory, B = the
-//                         K page in shared memory, K-major, 128-byte swizzle, 3-stage TMA ring),
-//                         online softmax by 128 threads (one row each, no shuffles), P (bf16) written
-//                         straight into CTA 1's shared memory over DSMEM in the MMA operand layout.
-//   CTA 1 ("value" CTA)   TMEM: O (512 columns).  O += P V per page (8 MMAs 128x256x16, A = P from shared
-//                         memory, B = the first 512 columns of the same page viewed MN-major, 3-stage
-//                         TMA ring), rare O rescale, epilogue (normalise, bf16 / fp32 split output).
+//   CTA 0 ("score" CTA)  S = Q K^T: 36 MMAs 128x128x16 per tile (N = 128 runs the tensor pipe at full
+//       rate, N = 64 does not).  Q is the A operand: dims 0..447 live in tensor memory (224 columns of
+//       packed bf16), dims 448..575 in shared memory; two S accumulators (2 x 128 columns).  K arrives
+//       through a 9-slot TMA ring whose slot is one 64-dim chunk of a tile ([128 tokens][64 dims],
+//       K-major, 128-byte swizzle), so a slot is refilled as soon as its four MMAs have retired.
+//       Two softmax warpgroups (one per page of the tile, one thread per row and page) exchange row
+//       maxima through shared memory, write P (bf16) in MMA operand layout to a staging buffer and
+//       push it to CTA 1 with bulk shared-to-shared copies that complete on CTA 1's barriers.
+//   CTA 1 ("value" CTA)  O += P V: per page 2 x 4 MMAs 128x256x16 (A = P from shared memory, B = the
+//       first 512 dims of the page viewed MN-major; 5-slot TMA ring of [64 tokens][256 dims]),
+//       the rare O rescale, and the epilogue (normalise; bf16 output or fp32 split partials).
 //
 // The tensor work divides 576 : 512 between the two SMs; each KV page is fetched from HBM by whichever
 // CTA asks first and from L2 by the other.  No TMA multicast is used.
@@ -37,38 +41,51 @@ namespace sm100 {
 using namespace ptx;
 
 constexpr int ROWS = 128;
-constexpr int TOK = 64;               // tokens per page / tile
+constexpr int PAGE = 64;              // tokens per page
 constexpr int D_QK = 576, D_V = 512;
 constexpr int BOX_BYTES = 8192;       // one TMA box: 64 tokens x 64 bf16, 128-byte swizzled rows
-constexpr int K_STAGE_BYTES = 9 * BOX_BYTES;
-constexpr int V_STAGE_BYTES = 8 * BOX_BYTES;
-constexpr int NSTAGE = 3;
-constexpr int P_BYTES = ROWS * TOK * 2;
-constexpr int NTHREADS = 256;
+constexpr int K_SLOT_BYTES = 2 * BOX_BYTES;   // [128 tokens][64 dims]
+constexpr int NKS = 9;                        // K ring slots (one tile = 9 chunks)
+constexpr int V_SLOT_BYTES = 4 * BOX_BYTES;   // [64 tokens][256 dims]
+constexpr int NVS = 5;                        // V ring slots
+constexpr int P_SUB_BYTES = ROWS * PAGE * 2;  // P of one page: [128 rows][64 tokens] bf16
+constexpr int NPB = 4;                        // P buffers in the value CTA: (tile parity, page of the tile)
+constexpr int SIDE_BYTES = 144;               // per warp and tile: 32 rescale factors + flag (+ pad)
+constexpr int NTHREADS = 384;
 constexpr long long WAIT_LIMIT = 2000000000LL;    // SM cycles (about one second)
 constexpr float RESCALE_THRESHOLD = 6.0f;         // log2 units
 
-// tensor-memory columns of the score CTA
-constexpr uint32_t TM_S0 = 0, TM_S1 = 64, TM_Q = 128;
+// tensor-memory columns of the score CTA: two S accumulators and the first 7 chunks of Q
+constexpr uint32_t TM_S = 0, TM_Q = 256;
+constexpr int Q_TMEM_CHUNKS = 7;
+
+// byte offsets inside Smem::data
+constexpr int SC_Q78 = 0;                                   // score CTA: Q dims 448..575, 2 x [128][64]
+constexpr int SC_KRING = SC_Q78 + 2 * 16384;
+constexpr int SC_STAGE = SC_KRING + NKS * K_SLOT_BYTES;     // 8 warps x 4 KB P staging
+constexpr int SC_SIDE = SC_STAGE + 8 * 4096;                // 4 warps x 144 B factor/flag staging
+constexpr int SC_XMAX = SC_SIDE + 4 * SIDE_BYTES;           // [2][2][128] floats
+constexpr int SC_END = SC_XMAX + 2 * 2 * ROWS * 4;
+constexpr int VA_VRING = 0;                                 // value CTA
+constexpr int VA_P = VA_VRING + NVS * V_SLOT_BYTES;
+constexpr int VA_END = VA_P + NPB * P_SUB_BYTES;
+constexpr int DATA_BYTES = VA_END > SC_END ? VA_END : SC_END;
 
 struct Smem {
-    // score CTA: 3 K stages (73,728 B each).  value CTA: 3 V stages (65,536 B each) + 2 P tiles.
-    uint8_t data[NSTAGE * V_STAGE_BYTES + 2 * P_BYTES];
-    float factor[2][ROWS];        // value CTA: per-row rescale factor that goes with P tile 0 / 1
-    uint32_t resc_flag[2][4];     // value CTA: "some row of this warp's 32 rows needs a rescale"
-    float fin_l[ROWS], fin_m[ROWS];   // value CTA: final row sum / running maximum of the request
-    uint64_t kv_full[NSTAGE], kv_empty[NSTAGE];
+    uint8_t data[DATA_BYTES];
+    uint8_t side[2][4][SIDE_BYTES];      // value CTA: factors + flag received with the first page of tile parity 0 / 1
+    float fin_l[2][ROWS], fin_m[ROWS];   // value CTA: final row sums (one per softmax warpgroup) / running maximum
+    uint64_t kv_full[NKS], kv_empty[NKS];
     uint64_t s_full[2], s_empty[2], q_ready;
-    uint64_t p_empty[2], fin_empty;                       // live in the score CTA, arrived by the value CTA
-    uint64_t p_full[2], pv_done[2], corr_done[2], fin_full;   // live in the value CTA
+    uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
+    uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
     uint32_t tmem_base;
     uint32_t aborted;
 };
 static_assert(sizeof(Smem) <= 232448, "shared memory budget");
-static_assert(NSTAGE * K_STAGE_BYTES <= NSTAGE * V_STAGE_BYTES + 2 * P_BYTES, "K ring must fit");
 
 struct Params {
-    int b, s_q, h_q, h_kv, g, rows, causal;
+    int b, s_q, h_q, h_kv, g, rows, causal, num_blocks;
     float scale_log2;
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
     __nv_bfloat16* out; int64_t o_sb, o_ss, o_sh;
@@ -82,7 +99,7 @@ struct Params {
 
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
-    int req, blk_begin, blk_end, seqlen, is_split, slot;
+    int req, blk_begin, blk_end, ntiles, seqlen, is_split, slot;
 };
 
 struct Walker {
@@ -96,8 +113,9 @@ struct Walker {
         w.req = req;
         w.seqlen = p.seqlens[req];
         w.blk_begin = req == m.begin_req_idx ? m.begin_block_idx : 0;
-        w.blk_end = req == m.end_req_idx ? m.end_block_idx : (w.seqlen + TOK - 1) / TOK;
+        w.blk_end = req == m.end_req_idx ? m.end_block_idx : (w.seqlen + PAGE - 1) / PAGE;
         if (w.blk_end < w.blk_begin) w.blk_end = w.blk_begin;
+        w.ntiles = (w.blk_end - w.blk_begin + 1) / 2;
         w.is_split = req == m.begin_req_idx ? m.is_first_req_splitted : (req == m.end_req_idx ? m.is_last_req_splitted : 0);
         w.slot = p.num_splits[req] + (req == m.begin_req_idx ? m.begin_split_idx : 0);
         return w;
@@ -121,6 +139,23 @@ struct Waiter {
         }
     }
 };
+
+#ifdef MLA_TRACE
+// Debug builds only: per-tile timestamps of every pipeline role of partition 0.
+__device__ unsigned long long g_trace[16][512];
+__device__ __forceinline__ void trace_ev(int part, int row_blk, int ev, uint32_t g) {
+    if (part == 0 && row_blk == 0 && g < 512) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_trace[ev][g] = t;
+    }
+}
+#define TRACE(ev, g) trace_ev(part, row_blk, ev, g)
+#define TRACE_CLOCK(ev, g) do { if (part == 0 && row_blk == 0 && (g) < 512) g_trace[ev][g] = (unsigned long long)clock64(); } while (0)
+#else
+#define TRACE(ev, g)
+#define TRACE_CLOCK(ev, g)
+#endif
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -149,18 +184,21 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
     }
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NSTAGE; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), 1); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
+        for (int i = 0; i < NKS; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), 1); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.s_full[i]), 1);
-            mbar_init(smem_addr(&sm.s_empty[i]), 128);
+            mbar_init(smem_addr(&sm.s_empty[i]), 256);
+            mbar_init(smem_addr(&sm.stage_free[i]), 1);
+        }
+        for (int i = 0; i < NPB; ++i) {
             mbar_init(smem_addr(&sm.p_empty[i]), 1);
-            mbar_init(smem_addr(&sm.p_full[i]), 128);
+            mbar_init(smem_addr(&sm.p_full[i]), 4);        // one arrive.expect_tx per sending warp
             mbar_init(smem_addr(&sm.pv_done[i]), 1);
             mbar_init(smem_addr(&sm.corr_done[i]), 128);
         }
-        mbar_init(smem_addr(&sm.q_ready), 128);
+        mbar_init(smem_addr(&sm.q_ready), 256);
         mbar_init(smem_addr(&sm.fin_empty), 128);
-        mbar_init(smem_addr(&sm.fin_full), 128);
+        mbar_init(smem_addr(&sm.fin_full), 256);
         sm.aborted = 0;
         fence_mbar_init();
         prefetch_tensormap(&kmap);
@@ -172,101 +210,137 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
     const uint32_t tmem = sm.tmem_base;
     Waiter wt(p.status, &sm.aborted);
+    const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
 
     // =====================================================================================================
     if (warp == 0) {
-        // ---------------- TMA producer (both CTAs): K pages (9 boxes) or V pages (8 boxes) --------------
+        // ---------------- TMA producer (both CTAs) ---------------------------------------------------------
         if (lane == 0) {
-            const int nbox = cta_rank == 0 ? 9 : 8;
-            const int stage_bytes = cta_rank == 0 ? K_STAGE_BYTES : V_STAGE_BYTES;
-            uint32_t g = 0;
+            uint32_t ks = 0;                               // ring slot counter (K chunks or V half-pages)
             for (Walker wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
-                int page_next = w.blk_begin < w.blk_end ? __ldg(bt + w.blk_begin) : 0;
-                for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
-                    const int page = page_next;
-                    if (blk + 1 < w.blk_end) page_next = __ldg(bt + blk + 1);
-                    const uint32_t stage = g % NSTAGE, ph = (g / NSTAGE) & 1;
-                    wt.wait<false>(&sm.kv_empty[stage], ph ^ 1, 1 + cta_rank * 100);
-                    const uint32_t bar = smem_addr(&sm.kv_full[stage]);
-                    mbar_arrive_expect_tx(bar, stage_bytes);
-                    const uint32_t dst = smem_addr(sm.data + stage * stage_bytes);
-                    for (int j = 0; j < nbox; ++j) tma_load_4d(dst + j * BOX_BYTES, &kmap, bar, j * 64, hk, 0, page);
+                for (int i = 0; i < w.ntiles; ++i) {
+                    const int blk0 = w.blk_begin + 2 * i;
+                    const int page0 = __ldg(bt + blk0);
+                    const int page1 = blk0 + 1 < w.blk_end ? __ldg(bt + blk0 + 1) : oob_page;
+                    if (cta_rank == 0) {
+                        for (int j = 0; j < 9; ++j, ++ks) {
+                            const uint32_t slot = ks % NKS;
+                            wt.wait<false>(&sm.kv_empty[slot], ((ks / NKS) & 1) ^ 1, 1);
+                            const uint32_t bar = smem_addr(&sm.kv_full[slot]);
+                            mbar_arrive_expect_tx(bar, K_SLOT_BYTES);
+                            const uint32_t dst = smem_addr(sm.data + SC_KRING + slot * K_SLOT_BYTES);
+                            tma_load_4d(dst, &kmap, bar, j * 64, hk, 0, page0);
+                            tma_load_4d(dst + BOX_BYTES, &kmap, bar, j * 64, hk, 0, page1);
+                        }
+                    } else {
+                        for (int h = 0; h < 2; ++h) {
+                            const int page = h ? page1 : page0;
+                            for (int nh = 0; nh < 2; ++nh, ++ks) {
+                                const uint32_t slot = ks % NVS;
+                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
+                                const uint32_t bar = smem_addr(&sm.kv_full[slot]);
+                                mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
+                                const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
+                                for (int j = 0; j < 4; ++j) tma_load_4d(dst + j * BOX_BYTES, &kmap, bar, (nh * 4 + j) * 64, hk, 0, page);
+                            }
+                        }
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer -----------------------------------------------------------------------
         if (lane == 0) {
-            uint32_t g = 0, nreq = 0;
+            uint32_t g = 0, ks = 0, nreq = 0;
             if (cta_rank == 0) {
-                constexpr uint32_t idesc = make_idesc_bf16(ROWS, TOK, false);
+                constexpr uint32_t idesc = make_idesc_bf16(ROWS, 128, false);
+                const uint32_t q78 = smem_addr(sm.data + SC_Q78);
                 for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     wt.wait<false>(&sm.q_ready, nreq & 1, 2);
-                    for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
-                        const uint32_t stage = g % NSTAGE, sb = g & 1;
-                        wt.wait<false>(&sm.kv_full[stage], (g / NSTAGE) & 1, 3);
+                    for (int i = 0; i < w.ntiles; ++i, ++g) {
+                        const uint32_t sb = g & 1;
                         wt.wait<false>(&sm.s_empty[sb], ((g >> 1) & 1) ^ 1, 4);
                         tc_fence_after();
-                        const uint32_t kbase = smem_addr(sm.data + stage * K_STAGE_BYTES);
-                        const uint32_t d_tmem = tmem + (sb ? TM_S1 : TM_S0);
-#pragma unroll 4
-                        for (int kk = 0; kk < D_QK / 16; ++kk) {
-                            const uint64_t bdesc = make_sw128_desc(kbase + (kk >> 2) * BOX_BYTES + (kk & 3) * 32, 16, 1024);
-                            mma_ts(d_tmem, tmem + TM_Q + kk * 8, bdesc, idesc, kk > 0);
+                        TRACE(1, g);
+                        TRACE_CLOCK(13, g);
+                        const uint32_t d_tmem = tmem + TM_S + sb * 128;
+                        for (int j = 0; j < 9; ++j, ++ks) {
+                            const uint32_t slot = ks % NKS;
+                            wt.wait<false>(&sm.kv_full[slot], (ks / NKS) & 1, 3);
+                            tc_fence_after();
+                            const uint32_t kbase = smem_addr(sm.data + SC_KRING + slot * K_SLOT_BYTES);
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; ++k4) {
+                                const uint64_t bdesc = make_sw128_desc(kbase + k4 * 32, 16, 1024);
+                                const uint32_t acc = (j > 0 || k4 > 0) ? 1u : 0u;
+                                if (j < Q_TMEM_CHUNKS) mma_ts(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, bdesc, idesc, acc);
+                                else mma_ss(d_tmem, make_sw128_desc(q78 + (j - Q_TMEM_CHUNKS) * 16384 + k4 * 32, 16, 1024), bdesc, idesc, acc);
+                            }
+                            tc_commit(smem_addr(&sm.kv_empty[slot]));
                         }
-                        tc_commit(smem_addr(&sm.kv_empty[stage]));
                         tc_commit(smem_addr(&sm.s_full[sb]));
+                        TRACE(2, g);
                     }
                 }
             } else {
                 constexpr uint32_t idesc = make_idesc_bf16(ROWS, 256, true);
                 for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
-                    for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
-                        const uint32_t stage = g % NSTAGE, pb = g & 1, pph = (g >> 1) & 1;
-                        wt.wait<false>(&sm.kv_full[stage], (g / NSTAGE) & 1, 103);
-                        wt.wait<true>(&sm.p_full[pb], pph, 104);
-                        wt.wait<false>(&sm.corr_done[pb], pph, 105);
-                        fence_proxy_async();
-                        tc_fence_after();
-                        const uint32_t vbase = smem_addr(sm.data + stage * V_STAGE_BYTES);
-                        const uint32_t pbase = smem_addr(sm.data + NSTAGE * V_STAGE_BYTES + pb * P_BYTES);
+                    for (int i = 0; i < w.ntiles; ++i, ++g) {
+                        for (int h = 0; h < 2; ++h) {
+                            const uint32_t pb = (g & 1) * 2 + h, pph = (g >> 1) & 1;
+                            wt.wait<true>(&sm.p_full[pb], pph, 104);
+                            TRACE(9, 2 * g + h);
+                            wt.wait<false>(&sm.corr_done[pb], pph, 105);
+                            fence_proxy_async();
+                            tc_fence_after();
+                            TRACE(10, 2 * g + h);
+                            const uint32_t pbase = smem_addr(sm.data + VA_P + pb * P_SUB_BYTES);
+                            for (int nh = 0; nh < 2; ++nh, ++ks) {
+                                const uint32_t slot = ks % NVS;
+                                wt.wait<false>(&sm.kv_full[slot], (ks / NVS) & 1, 103);
+                                tc_fence_after();
+                                const uint32_t vbase = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
 #pragma unroll
-                        for (int kt = 0; kt < TOK / 16; ++kt) {
-                            const uint64_t adesc = make_sw128_desc(pbase + kt * 32, 16, 1024);
-#pragma unroll
-                            for (int nh = 0; nh < 2; ++nh) {
-                                const uint64_t bdesc = make_sw128_desc(vbase + nh * 4 * BOX_BYTES + kt * 2048, BOX_BYTES, 1024);
-                                mma_ss(tmem + nh * 256, adesc, bdesc, idesc, (blk > w.blk_begin || kt > 0) ? 1u : 0u);
+                                for (int kt = 0; kt < PAGE / 16; ++kt) {
+                                    const uint64_t adesc = make_sw128_desc(pbase + kt * 32, 16, 1024);
+                                    const uint64_t bdesc = make_sw128_desc(vbase + kt * 2048, BOX_BYTES, 1024);
+                                    mma_ss(tmem + nh * 256, adesc, bdesc, idesc, (i > 0 || h > 0 || kt > 0) ? 1u : 0u);
+                                }
+                                tc_commit(smem_addr(&sm.kv_empty[slot]));
                             }
+                            tc_commit(smem_addr(&sm.pv_done[pb]));
                         }
-                        tc_commit(smem_addr(&sm.kv_empty[stage]));
-                        tc_commit(smem_addr(&sm.pv_done[pb]));
                     }
                 }
             }
         }
     } else if (warp == 2) {
-        // ---------------- value CTA: tell the score CTA when a P tile has been consumed -------------------
+        // ---------------- value CTA: tell the score CTA when a P buffer has been consumed ------------------
         if (cta_rank == 1 && lane == 0) {
             uint32_t g = 0;
-            const uint32_t remote_p_empty0 = map_to_cta(smem_addr(&sm.p_empty[0]), 0);
-            const uint32_t remote_p_empty1 = map_to_cta(smem_addr(&sm.p_empty[1]), 0);
+            uint32_t remote_p_empty[NPB];
+            for (int i = 0; i < NPB; ++i) remote_p_empty[i] = map_to_cta(smem_addr(&sm.p_empty[i]), 0);
             for (Walker wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
-                for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
-                    const uint32_t pb = g & 1;
-                    wt.wait<false>(&sm.pv_done[pb], (g >> 1) & 1, 106);
-                    mbar_arrive_remote(pb ? remote_p_empty1 : remote_p_empty0);
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t pb = (g & 1) * 2 + h;
+                        wt.wait<false>(&sm.pv_done[pb], (g >> 1) & 1, 106);
+                        TRACE(11, 2 * g + h);
+                        mbar_arrive_remote(remote_p_empty[pb]);
+                    }
                 }
             }
         }
     } else if (warp >= 4) {
-        const int r = (warp & 3) * 32 + lane;                     // row inside the block = TMEM lane
-        const uint32_t tlane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int wq = warp & 3;                                  // TMEM lane quarter of this warp
+        const int half = (warp - 4) >> 2;                         // score CTA: page of the tile this warpgroup owns
+        const int r = wq * 32 + lane;                             // row inside the block = TMEM lane
+        const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
         const int row = row_blk * ROWS + r;                       // row inside the (request, kv head) group
         const bool row_ok = row < p.rows;
         const int t = row_ok ? row / p.g : 0;
@@ -274,26 +348,31 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
         uint32_t g = 0, nreq = 0;
 
         if (cta_rank == 0) {
-            // ---------------- softmax warpgroup of the score CTA ---------------------------------------------
-            const uint32_t remote_p = map_to_cta(smem_addr(sm.data + NSTAGE * V_STAGE_BYTES), 1);
-            const uint32_t remote_factor = map_to_cta(smem_addr(&sm.factor[0][0]), 1);
-            const uint32_t remote_flag = map_to_cta(smem_addr(&sm.resc_flag[0][0]), 1);
-            const uint32_t remote_p_full0 = map_to_cta(smem_addr(&sm.p_full[0]), 1);
-            const uint32_t remote_p_full1 = map_to_cta(smem_addr(&sm.p_full[1]), 1);
-            const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[r]), 1);
+            // ---------------- softmax warpgroups of the score CTA --------------------------------------------
+            uint8_t* stage = sm.data + SC_STAGE + (half * 4 + wq) * 4096;
+            float* side_src = reinterpret_cast<float*>(sm.data + SC_SIDE + wq * SIDE_BYTES);
+            float* xmax = reinterpret_cast<float*>(sm.data + SC_XMAX);
+            const uint32_t remote_p = map_to_cta(smem_addr(sm.data + VA_P), 1) + wq * 4096;
+            const uint32_t remote_side = map_to_cta(smem_addr(&sm.side[0][wq][0]), 1);
+            uint32_t remote_p_full[NPB];
+            for (int i = 0; i < NPB; ++i) remote_p_full[i] = map_to_cta(smem_addr(&sm.p_full[i]), 1);
+            const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[half][r]), 1);
             const uint32_t remote_fin_m = map_to_cta(smem_addr(&sm.fin_m[r]), 1);
             const uint32_t remote_fin_full = map_to_cta(smem_addr(&sm.fin_full), 1);
             for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
-                // Q row -> tensor memory (A operand: 2 bf16 per 32-bit column).  Every MMA that read the previous
-                // request's Q has completed: this thread saw s_full of that request's last tile.
+                // ---- Q row -> A operand: chunks 0..6 to tensor memory (2 bf16 per 32-bit column), chunks 7, 8 to shared
+                // memory (K-major, 128-byte swizzle).  Warpgroup 0 takes chunks 0-3 and 7, warpgroup 1 chunks 4-6 and 8.
+                // Every MMA that read the previous request's Q has completed: this thread saw s_full of its last tile.
                 {
                     const __nv_bfloat16* qrow = p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
+                    const int c_begin = half ? 4 : 0, c_end = half ? 7 : 4, c_smem = half ? 8 : 7;
 #pragma unroll 1
-                    for (int c = 0; c < D_QK / 64; ++c) {
+                    for (int c = c_begin; c <= c_end; ++c) {
+                        const int chunk = c < c_end ? c : c_smem;
                         uint32_t v[32];
                         if (row_ok) {
-                            const uint4* src = reinterpret_cast<const uint4*>(qrow + c * 64);
+                            const uint4* src = reinterpret_cast<const uint4*>(qrow + chunk * 64);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 const uint4 x = __ldg(src + i);
@@ -303,42 +382,55 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
 #pragma unroll
                             for (int i = 0; i < 32; ++i) v[i] = 0u;
                         }
-                        tmem_st32(tlane + TM_Q + c * 32, v);
+                        if (c < c_end) {
+                            tmem_st32(tlane + TM_Q + chunk * 32, v);
+                        } else {
+                            uint8_t* qdst = sm.data + SC_Q78 + (chunk - Q_TMEM_CHUNKS) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+                            for (int ch = 0; ch < 8; ++ch)
+                                *reinterpret_cast<uint4*>(qdst + ((ch ^ (r & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+                        }
                     }
                     tmem_wait_st();
+                    fence_proxy_async_smem();
                     tc_fence_before();
                     mbar_arrive(smem_addr(&sm.q_ready));
                 }
-                // first key position this row must NOT see
-                const int limit = p.causal ? w.seqlen - (p.s_q - 1 - t) : w.seqlen;
+                // first key position this row must NOT see (causal limit, and the end of this partition's range)
+                const int limit = min(p.causal ? w.seqlen - (p.s_q - 1 - t) : w.seqlen, w.blk_end * PAGE);
                 float m_run = -INFINITY, l_run = 0.f;
-                for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t sb = g & 1, ph = (g >> 1) & 1;
                     wt.wait<false>(&sm.s_full[sb], ph, 5);
                     tc_fence_after();
+                    if (threadIdx.x == 128) TRACE(3, g);
                     uint32_t s[64];
                     {
                         uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[0]);
                         uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[32]);
-                        tmem_ld32(tlane + (sb ? TM_S1 : TM_S0), lo);
-                        tmem_ld32(tlane + (sb ? TM_S1 : TM_S0) + 32, hi);
+                        tmem_ld32(tlane + TM_S + sb * 128 + half * 64, lo);
+                        tmem_ld32(tlane + TM_S + sb * 128 + half * 64 + 32, hi);
                     }
                     tmem_wait_ld();
                     tc_fence_before();
-                    mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S buffer
+                    mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
-                    const int nvalid = limit - blk * TOK;             // columns [0, nvalid) are visible
+                    const int nvalid = limit - (w.blk_begin + 2 * i + half) * PAGE;   // columns [0, nvalid) are visible
                     float mx = -INFINITY;
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const float v = i < nvalid ? __uint_as_float(s[i]) : -INFINITY;
-                        s[i] = __float_as_uint(v);
+                    for (int c = 0; c < 64; ++c) {
+                        const float v = c < nvalid ? __uint_as_float(s[c]) : -INFINITY;
+                        s[c] = __float_as_uint(v);
                         mx = fmaxf(mx, v);
                     }
+                    // the row maximum over both pages of the tile
+                    xmax[((g & 1) * 2 + half) * ROWS + r] = mx;
+                    named_bar_sync(1, 256);
+                    mx = fmaxf(mx, xmax[((g & 1) * 2 + (half ^ 1)) * ROWS + r]);
                     mx *= p.scale_log2;                                // scale > 0: max commutes with scaling
                     float factor = 1.f;
                     bool resc = false;
-                    if (blk == w.blk_begin) {
+                    if (i == 0) {
                         m_run = mx;
                     } else if (mx > m_run + RESCALE_THRESHOLD) {
                         factor = ex2(m_run - mx);                      // m_run = -inf -> 0
@@ -350,80 +442,112 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     uint32_t pk[32];
                     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 64; i += 2) {
-                        const float e0 = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_m));
-                        const float e1 = ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_m));
+                    for (int c = 0; c < 64; c += 2) {
+                        const float e0 = ex2(fmaf(__uint_as_float(s[c]), p.scale_log2, neg_m));
+                        const float e1 = ex2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, neg_m));
                         sum0 += e0; sum1 += e1;
-                        pk[i >> 1] = pack_bf16(e0, e1);
+                        pk[c >> 1] = pack_bf16(e0, e1);
                     }
                     l_run += sum0 + sum1;
                     const bool any_resc = __any_sync(0xffffffffu, resc);
+                    if (threadIdx.x == 128) TRACE(4, g);
 
-                    wt.wait<true>(&sm.p_empty[sb], ph ^ 1, 6);        // P tile `sb` of the value CTA is free
-                    const uint32_t prow = remote_p + sb * P_BYTES + (r >> 3) * 1024 + (r & 7) * 128;
+                    // staging of this warp is free once the previous tile's copy has landed in the value CTA
+                    wt.wait<true>(&sm.stage_free[half], (g & 1) ^ 1, 8);
+                    {
+                        uint8_t* prow = stage + (lane >> 3) * 1024 + (lane & 7) * 128;
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch)
-                        st_cluster_v4(prow + ((ch ^ (r & 7)) << 4), pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-                    st_cluster_f32(remote_factor + (sb * ROWS + r) * 4, factor);
-                    if (lane == 0) st_cluster_u32(remote_flag + (sb * 4 + (warp & 3)) * 4, any_resc ? 1u : 0u);
-                    fence_proxy_async();
-                    mbar_arrive_remote(sb ? remote_p_full1 : remote_p_full0);
+                        for (int ch = 0; ch < 8; ++ch)
+                            *reinterpret_cast<uint4*>(prow + ((ch ^ (lane & 7)) << 4)) = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+                        if (half == 0) {
+                            side_src[lane] = factor;
+                            if (lane == 0) reinterpret_cast<uint32_t*>(side_src)[32] = any_resc ? 1u : 0u;
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const uint32_t pb = (g & 1) * 2 + half;
+                        wt.wait<true>(&sm.p_empty[pb], ph ^ 1, 6);    // that P buffer of the value CTA has been consumed
+                        if (threadIdx.x == 128) TRACE(5, g);
+                        mbar_arrive_expect_tx_remote(remote_p_full[pb], 4096 + (half == 0 ? SIDE_BYTES : 0));
+                        bulk_copy_to_cluster(remote_p + pb * P_SUB_BYTES, smem_addr(stage), 4096, remote_p_full[pb]);
+                        if (half == 0)
+                            bulk_copy_to_cluster(remote_side + (g & 1) * 4 * SIDE_BYTES, smem_addr(side_src), SIDE_BYTES, remote_p_full[pb]);
+                        if (threadIdx.x == 128) TRACE(6, g);
+                    }
+                    __syncwarp();
                 }
                 // final statistics of this request for the epilogue in the value CTA
                 wt.wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
                 st_cluster_f32(remote_fin_l, l_run);
-                st_cluster_f32(remote_fin_m, m_run);
+                if (half == 0) st_cluster_f32(remote_fin_m, m_run);
                 mbar_arrive_remote(remote_fin_full);
             }
-        } else {
+        } else if (warp < 8) {
             // ---------------- correction / epilogue warpgroup of the value CTA ---------------------------------
             const uint32_t remote_fin_empty = map_to_cta(smem_addr(&sm.fin_empty), 0);
+            const uint32_t remote_stage_free0 = map_to_cta(smem_addr(&sm.stage_free[0]), 0);
+            const uint32_t remote_stage_free1 = map_to_cta(smem_addr(&sm.stage_free[1]), 0);
+            uint32_t vs = 0;                                          // V ring slot counter
             for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
-                for (int blk = w.blk_begin; blk < w.blk_end; ++blk, ++g) {
-                    const uint32_t pb = g & 1, ph = (g >> 1) & 1;
-                    wt.wait<true>(&sm.p_full[pb], ph, 107);
-                    const bool need = blk > w.blk_begin && sm.resc_flag[pb][warp & 3] != 0;    // warp-uniform
-                    if (need) {
-                        // every earlier PV MMA has finished before O is touched
-                        wt.wait<false>(&sm.pv_done[pb ^ 1], ((g - 1) >> 1) & 1, 108);
-                        tc_fence_after();
-                        const float f = sm.factor[pb][r];
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
+                    for (int h = 0; h < 2; ++h, vs += 2) {
+                        const uint32_t pb = (g & 1) * 2 + h, ph = (g >> 1) & 1;
+                        wt.wait<true>(&sm.p_full[pb], ph, 107);
+                        if (threadIdx.x == 128) {
+                            TRACE(12, 2 * g + h);
+                            mbar_arrive_remote(h ? remote_stage_free1 : remote_stage_free0);   // the copy has landed
+                        }
+                        if (h == 0 && i > 0) {
+                            const float* side = reinterpret_cast<const float*>(&sm.side[g & 1][wq][0]);
+                            const bool need = reinterpret_cast<const uint32_t*>(side)[32] != 0;    // warp-uniform
+                            if (need) {
+                                // every earlier PV MMA has finished before O is touched
+                                wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 108);
+                                tc_fence_after();
+                                const float f = side[lane];
 #pragma unroll 1
-                        for (int c = 0; c < D_V / 32; ++c) {
-                            uint32_t v[32];
-                            tmem_ld32(tlane + c * 32, v);
-                            tmem_wait_ld();
+                                for (int c = 0; c < D_V / 32; ++c) {
+                                    uint32_t v[32];
+                                    tmem_ld32(tlane + c * 32, v);
+                                    tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                            tmem_st32(tlane + c * 32, v);
+                                    for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * f);
+                                    tmem_st32(tlane + c * 32, v);
+                                }
+                                tmem_wait_st();
+                            }
                         }
-                        tmem_wait_st();
-                    }
-                    // Tokens at or beyond the sequence length may hold anything (NaN included) in the cache:
-                    // their probabilities are zero, so their V rows are zeroed to keep 0 * NaN out of O.
-                    const int nvalid = w.seqlen - blk * TOK;
-                    if (nvalid < TOK) {
-                        const uint32_t stage = g % NSTAGE;
-                        wt.wait<false>(&sm.kv_full[stage], (g / NSTAGE) & 1, 109);
-                        uint8_t* vst = sm.data + stage * V_STAGE_BYTES;
-                        const int nz = (TOK - max(nvalid, 0)) * 8 * 8;      // rows x boxes x 16-byte chunks
-                        const int tid = threadIdx.x - 128;
-                        for (int i = tid; i < nz; i += 128) {
-                            const int chunk = i & 7, box = (i >> 3) & 7, rr = max(nvalid, 0) + (i >> 6);
-                            *reinterpret_cast<uint4*>(vst + box * BOX_BYTES + rr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                        // Tokens at or beyond the sequence length may hold anything (NaN included) in a real page:
+                        // their probabilities are zero, so their V rows are zeroed to keep 0 * NaN out of O.
+                        const int blk = w.blk_begin + 2 * i + h;
+                        const int nvalid = w.seqlen - blk * PAGE;
+                        if (blk < w.blk_end && nvalid < PAGE) {
+                            const int first = max(nvalid, 0);
+                            for (int nh = 0; nh < 2; ++nh) {
+                                const uint32_t slot = (vs + nh) % NVS;
+                                wt.wait<false>(&sm.kv_full[slot], ((vs + nh) / NVS) & 1, 109);
+                                uint8_t* vst = sm.data + VA_VRING + slot * V_SLOT_BYTES;
+                                const int nz = (PAGE - first) * 4 * 8;              // rows x boxes x 16-byte chunks
+                                for (int k = threadIdx.x - 128; k < nz; k += 128) {
+                                    const int chunk = k & 7, box = (k >> 3) & 3, rr = first + (k >> 5);
+                                    *reinterpret_cast<uint4*>(vst + box * BOX_BYTES + rr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                                }
+                            }
+                            fence_proxy_async();
                         }
-                        fence_proxy_async();
+                        tc_fence_before();
+                        mbar_arrive(smem_addr(&sm.corr_done[pb]));
                     }
-                    tc_fence_before();
-                    mbar_arrive(smem_addr(&sm.corr_done[pb]));
                 }
                 // ---- epilogue -----------------------------------------------------------------------------------
-                const bool has_tiles = w.blk_end > w.blk_begin;
-                if (has_tiles) wt.wait<false>(&sm.pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, 110);
+                const bool has_tiles = w.ntiles > 0;
+                if (has_tiles) wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 110);
                 wt.wait<true>(&sm.fin_full, nreq & 1, 111);
                 tc_fence_after();
-                const float L = sm.fin_l[r], M = sm.fin_m[r];
+                const float L = sm.fin_l[0][r] + sm.fin_l[1][r], M = sm.fin_m[r];
                 const bool empty = !(L > 0.f) || !has_tiles;          // also catches NaN
                 const float scale = empty ? 0.f : 1.f / L;
                 if (!w.is_split) {
@@ -434,13 +558,13 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                         if (has_tiles) { tmem_ld32(tlane + c * 32, v); tmem_wait_ld(); }
                         if (row_ok) {
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
+                            for (int k = 0; k < 4; ++k) {
                                 uint4 o;
-                                o.x = empty ? 0u : pack_bf16(__uint_as_float(v[8 * i]) * scale, __uint_as_float(v[8 * i + 1]) * scale);
-                                o.y = empty ? 0u : pack_bf16(__uint_as_float(v[8 * i + 2]) * scale, __uint_as_float(v[8 * i + 3]) * scale);
-                                o.z = empty ? 0u : pack_bf16(__uint_as_float(v[8 * i + 4]) * scale, __uint_as_float(v[8 * i + 5]) * scale);
-                                o.w = empty ? 0u : pack_bf16(__uint_as_float(v[8 * i + 6]) * scale, __uint_as_float(v[8 * i + 7]) * scale);
-                                *reinterpret_cast<uint4*>(orow + c * 32 + i * 8) = o;
+                                o.x = empty ? 0u : pack_bf16(__uint_as_float(v[8 * k]) * scale, __uint_as_float(v[8 * k + 1]) * scale);
+                                o.y = empty ? 0u : pack_bf16(__uint_as_float(v[8 * k + 2]) * scale, __uint_as_float(v[8 * k + 3]) * scale);
+                                o.z = empty ? 0u : pack_bf16(__uint_as_float(v[8 * k + 4]) * scale, __uint_as_float(v[8 * k + 5]) * scale);
+                                o.w = empty ? 0u : pack_bf16(__uint_as_float(v[8 * k + 6]) * scale, __uint_as_float(v[8 * k + 7]) * scale);
+                                *reinterpret_cast<uint4*>(orow + c * 32 + k * 8) = o;
                             }
                         }
                     }
@@ -454,13 +578,13 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                         if (has_tiles) { tmem_ld32(tlane + c * 32, v); tmem_wait_ld(); }
                         if (row_ok) {
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
+                            for (int k = 0; k < 8; ++k) {
                                 float4 o;
-                                o.x = empty ? 0.f : __uint_as_float(v[4 * i]) * scale;
-                                o.y = empty ? 0.f : __uint_as_float(v[4 * i + 1]) * scale;
-                                o.z = empty ? 0.f : __uint_as_float(v[4 * i + 2]) * scale;
-                                o.w = empty ? 0.f : __uint_as_float(v[4 * i + 3]) * scale;
-                                *reinterpret_cast<float4*>(orow + c * 32 + i * 4) = o;
+                                o.x = empty ? 0.f : __uint_as_float(v[4 * k]) * scale;
+                                o.y = empty ? 0.f : __uint_as_float(v[4 * k + 1]) * scale;
+                                o.z = empty ? 0.f : __uint_as_float(v[4 * k + 2]) * scale;
+                                o.w = empty ? 0.f : __uint_as_float(v[4 * k + 3]) * scale;
+                                *reinterpret_cast<float4*>(orow + c * 32 + k * 4) = o;
                             }
                         }
                     }
@@ -502,6 +626,12 @@ static EncodeTiledFn get_encode_fn() {
 
 }  // namespace sm100
 
+#ifdef MLA_TRACE
+extern "C" int mla_debug_trace_copy(void* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_trace, sizeof(sm100::g_trace));
+}
+#endif
+
 bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
     if (a.d_qk != 576 || a.d_v != 512 || a.page_block_size != 64) return false;
     if (a.h_kv <= 0 || a.h_q % a.h_kv != 0) return false;
@@ -513,6 +643,7 @@ bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
     const int rows = a.s_q * (a.h_q / a.h_kv);
     const int64_t row_blocks = (rows + 127) / 128;
     if (row_blocks * a.h_kv > 65535 || a.num_sm_parts > 65535) return false;
+    if (!(a.softmax_scale > 0.f)) return false;       // the row maximum is taken before scaling
     return true;
 }
 
@@ -543,6 +674,7 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     p.meta = a.meta; p.num_splits = a.num_splits; p.lse_accum = a.lse_accum; p.o_accum = a.o_accum;
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
+    p.num_blocks = a.num_blocks;
 
     static bool configured[64] = {};
     int dev = 0;
