@@ -10,8 +10,9 @@
 //   CTA 0 ("score" CTA)  S = Q K^T: 36 MMAs 128x128x16 per tile (N = 128 runs the tensor pipe at full
 //       rate, N = 64 does not).  Q is the A operand: dims 0..447 live in tensor memory (224 columns of
 //       packed bf16), dims 448..575 in shared memory; two S accumulators (2 x 128 columns).  K arrives
-//       through a 9-slot TMA ring whose slot is one 64-dim chunk of a tile ([128 tokens][64 dims],
-//       K-major, 128-byte swizzle), so a slot is refilled as soon as its four MMAs have retired.
+//       through a TMA ring of three 48 KB groups; a group is three 64-dim chunks of a tile (each
+//       [128 tokens][64 dims], K-major, 128-byte swizzle) and is refilled as soon as its twelve MMAs
+//       have retired.
 //       Two softmax warpgroups (one per page of the tile, one thread per row and page) exchange row
 //       maxima through shared memory, write P (bf16) in MMA operand layout to a staging buffer and
 //       push it to CTA 1 with bulk shared-to-shared copies that complete on CTA 1's barriers.
@@ -44,12 +45,14 @@ constexpr int ROWS = 128;
 constexpr int PAGE = 64;              // tokens per page
 constexpr int D_QK = 576, D_V = 512;
 constexpr int BOX_BYTES = 8192;       // one TMA box: 64 tokens x 64 bf16, 128-byte swizzled rows
-constexpr int K_SLOT_BYTES = 2 * BOX_BYTES;   // [128 tokens][64 dims]
-constexpr int NKS = 9;                        // K ring slots (one tile = 9 chunks)
-constexpr int V_SLOT_BYTES = 4 * BOX_BYTES;   // [64 tokens][256 dims]
+constexpr int K_CHUNK_BYTES = 2 * BOX_BYTES;  // one 64-dim chunk of a tile: [128 tokens][64 dims]
+constexpr int K_GROUP_BYTES = 3 * K_CHUNK_BYTES;   // the K ring moves in groups of 3 chunks (one barrier pair per group)
+constexpr int NKS = 3;                        // K ring slots = groups per tile: group j of every tile uses slot j
+constexpr int V_SLOT_BYTES = 4 * BOX_BYTES;   // half a page of V: [64 tokens][256 dims] as 4 boxes
 constexpr int NVS = 5;                        // V ring slots
 constexpr int P_SUB_BYTES = ROWS * PAGE * 2;  // P of one page: [128 rows][64 tokens] bf16
 constexpr int NPB = 4;                        // P buffers in the value CTA: (tile parity, page of the tile)
+constexpr int NRING = NKS > NVS ? NKS : NVS;
 constexpr int SIDE_BYTES = 144;               // per warp and tile: 32 rescale factors + flag (+ pad)
 constexpr int NTHREADS = 384;
 constexpr long long WAIT_LIMIT = 2000000000LL;    // SM cycles (about one second)
@@ -62,7 +65,7 @@ constexpr int Q_TMEM_CHUNKS = 7;
 // byte offsets inside Smem::data
 constexpr int SC_Q78 = 0;                                   // score CTA: Q dims 448..575, 2 x [128][64]
 constexpr int SC_KRING = SC_Q78 + 2 * 16384;
-constexpr int SC_STAGE = SC_KRING + NKS * K_SLOT_BYTES;     // 8 warps x 4 KB P staging
+constexpr int SC_STAGE = SC_KRING + NKS * K_GROUP_BYTES;     // 8 warps x 4 KB P staging
 constexpr int SC_SIDE = SC_STAGE + 8 * 4096;                // 4 warps x 144 B factor/flag staging
 constexpr int SC_XMAX = SC_SIDE + 4 * SIDE_BYTES;           // [2][2][128] floats
 constexpr int SC_END = SC_XMAX + 2 * 2 * ROWS * 4;
@@ -75,8 +78,8 @@ struct Smem {
     uint8_t data[DATA_BYTES];
     uint8_t side[2][4][SIDE_BYTES];      // value CTA: factors + flag received with the first page of tile parity 0 / 1
     float fin_l[2][ROWS], fin_m[ROWS];   // value CTA: final row sums (one per softmax warpgroup) / running maximum
-    uint64_t kv_full[NKS], kv_empty[NKS];
-    uint64_t s_full[2], s_empty[2], q_ready;
+    uint64_t kv_full[NRING], kv_empty[NRING];     // K groups (score CTA) / V slots (value CTA)
+    uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
     uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
     uint32_t tmem_base;
@@ -184,15 +187,16 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
     }
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NKS; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), 1); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
+        for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), 1); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.s_full[i]), 1);
             mbar_init(smem_addr(&sm.s_empty[i]), 256);
             mbar_init(smem_addr(&sm.stage_free[i]), 1);
+            mbar_init(smem_addr(&sm.stage_full[i]), 128);
         }
         for (int i = 0; i < NPB; ++i) {
             mbar_init(smem_addr(&sm.p_empty[i]), 1);
-            mbar_init(smem_addr(&sm.p_full[i]), 4);        // one arrive.expect_tx per sending warp
+            mbar_init(smem_addr(&sm.p_full[i]), 1);        // one arrive.expect_tx by the sending thread
             mbar_init(smem_addr(&sm.pv_done[i]), 1);
             mbar_init(smem_addr(&sm.corr_done[i]), 128);
         }
@@ -200,6 +204,9 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
         mbar_init(smem_addr(&sm.fin_empty), 128);
         mbar_init(smem_addr(&sm.fin_full), 256);
         sm.aborted = 0;
+        // first use of every P buffer: its arrival and expected byte count are armed here (matters in the value CTA)
+        for (int i = 0; i < NPB; ++i)
+            mbar_arrive_expect_tx(smem_addr(&sm.p_full[i]), P_SUB_BYTES + ((i & 1) == 0 ? 4 * SIDE_BYTES : 0));
         fence_mbar_init();
         prefetch_tensormap(&kmap);
     }
@@ -220,19 +227,32 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             for (Walker wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
+                // page ids are fetched one tile ahead so the block-table latency stays off the TMA issue path
+                int nxt0 = 0, nxt1 = oob_page;
+                if (w.ntiles > 0) {
+                    nxt0 = __ldg(bt + w.blk_begin);
+                    nxt1 = w.blk_begin + 1 < w.blk_end ? __ldg(bt + w.blk_begin + 1) : oob_page;
+                }
                 for (int i = 0; i < w.ntiles; ++i) {
-                    const int blk0 = w.blk_begin + 2 * i;
-                    const int page0 = __ldg(bt + blk0);
-                    const int page1 = blk0 + 1 < w.blk_end ? __ldg(bt + blk0 + 1) : oob_page;
+                    const int page0 = nxt0, page1 = nxt1;
+                    if (i + 1 < w.ntiles) {
+                        const int nb = w.blk_begin + 2 * (i + 1);
+                        nxt0 = __ldg(bt + nb);
+                        nxt1 = nb + 1 < w.blk_end ? __ldg(bt + nb + 1) : oob_page;
+                    }
                     if (cta_rank == 0) {
-                        for (int j = 0; j < 9; ++j, ++ks) {
-                            const uint32_t slot = ks % NKS;
-                            wt.wait<false>(&sm.kv_empty[slot], ((ks / NKS) & 1) ^ 1, 1);
-                            const uint32_t bar = smem_addr(&sm.kv_full[slot]);
-                            mbar_arrive_expect_tx(bar, K_SLOT_BYTES);
-                            const uint32_t dst = smem_addr(sm.data + SC_KRING + slot * K_SLOT_BYTES);
-                            tma_load_4d(dst, &kmap, bar, j * 64, hk, 0, page0);
-                            tma_load_4d(dst + BOX_BYTES, &kmap, bar, j * 64, hk, 0, page1);
+                        for (int grp = 0; grp < 3; ++grp, ++ks) {
+                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 1);
+                            if (grp == 0) TRACE(0, ks / 3);
+                            if (grp == 2) TRACE(7, ks / 3);
+                            const uint32_t bar = smem_addr(&sm.kv_full[grp]);
+                            mbar_arrive_expect_tx(bar, K_GROUP_BYTES);
+                            const uint32_t dst = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES);
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) {
+                                tma_load_4d(dst + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, hk, 0, page0);
+                                tma_load_4d(dst + c * K_CHUNK_BYTES + BOX_BYTES, &kmap, bar, (grp * 3 + c) * 64, hk, 0, page1);
+                            }
                         }
                     } else {
                         for (int h = 0; h < 2; ++h) {
@@ -243,6 +263,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                                 const uint32_t bar = smem_addr(&sm.kv_full[slot]);
                                 mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
                                 const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
+#pragma unroll
                                 for (int j = 0; j < 4; ++j) tma_load_4d(dst + j * BOX_BYTES, &kmap, bar, (nh * 4 + j) * 64, hk, 0, page);
                             }
                         }
@@ -254,9 +275,13 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
         // ---------------- MMA issuer -----------------------------------------------------------------------
         if (lane == 0) {
             uint32_t g = 0, ks = 0, nreq = 0;
+            (void)ks;
             if (cta_rank == 0) {
                 constexpr uint32_t idesc = make_idesc_bf16(ROWS, 128, false);
-                const uint32_t q78 = smem_addr(sm.data + SC_Q78);
+                const uint32_t q78_lo = sw128_desc_lo(smem_addr(sm.data + SC_Q78), 16);
+                const uint32_t kring_lo = sw128_desc_lo(smem_addr(sm.data + SC_KRING), 16);
+                const uint32_t kv_empty0 = smem_addr(&sm.kv_empty[0]);
+                const uint32_t kv_full0 = smem_addr(&sm.kv_full[0]);
                 for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     wt.wait<false>(&sm.q_ready, nreq & 1, 2);
@@ -267,19 +292,33 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                         TRACE(1, g);
                         TRACE_CLOCK(13, g);
                         const uint32_t d_tmem = tmem + TM_S + sb * 128;
-                        for (int j = 0; j < 9; ++j, ++ks) {
-                            const uint32_t slot = ks % NKS;
-                            wt.wait<false>(&sm.kv_full[slot], (ks / NKS) & 1, 3);
-                            tc_fence_after();
-                            const uint32_t kbase = smem_addr(sm.data + SC_KRING + slot * K_SLOT_BYTES);
+                        // Group j of every tile lives in ring slot j, parity = tile parity.  Descriptors advance by
+                        // 32-bit adds only and the loop is fully unrolled: one thread issues everything, so its
+                        // instruction latency is the issue rate.
+                        constexpr uint32_t hi = sw128_desc_hi(1024);
+                        // The probe of the next group's barrier is issued before this group's MMAs so that its
+                        // latency hides behind them (the MMA queue is shallow: time the issuing thread spends
+                        // waiting is time the tensor pipe idles).
+                        bool ready = mbar_try_wait(kv_full0, g & 1);
 #pragma unroll
-                            for (int k4 = 0; k4 < 4; ++k4) {
-                                const uint64_t bdesc = make_sw128_desc(kbase + k4 * 32, 16, 1024);
-                                const uint32_t acc = (j > 0 || k4 > 0) ? 1u : 0u;
-                                if (j < Q_TMEM_CHUNKS) mma_ts(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, bdesc, idesc, acc);
-                                else mma_ss(d_tmem, make_sw128_desc(q78 + (j - Q_TMEM_CHUNKS) * 16384 + k4 * 32, 16, 1024), bdesc, idesc, acc);
+                        for (int grp = 0; grp < 3; ++grp) {
+                            if (!ready) wt.wait<false>(&sm.kv_full[grp], g & 1, 3);
+                            tc_fence_after();
+                            if (grp == 0) TRACE(8, g);
+                            if (grp == 2) TRACE(14, g);
+                            if (grp < 2) ready = mbar_try_wait(kv_full0 + (grp + 1) * 8, g & 1);
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) {
+                                const int j = grp * 3 + c;
+                                const uint32_t b_lo = kring_lo + j * (K_CHUNK_BYTES >> 4);
+#pragma unroll
+                                for (int k4 = 0; k4 < 4; ++k4) {
+                                    const uint32_t acc = (j > 0 || k4 > 0) ? 1u : 0u;
+                                    if (j < Q_TMEM_CHUNKS) mma_ts_lohi(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, b_lo + k4 * 2, hi, idesc, acc);
+                                    else mma_ss_lohi(d_tmem, q78_lo + (j - Q_TMEM_CHUNKS) * (16384 >> 4) + k4 * 2, hi, b_lo + k4 * 2, hi, idesc, acc);
+                                }
                             }
-                            tc_commit(smem_addr(&sm.kv_empty[slot]));
+                            tc_commit(kv_empty0 + grp * 8);
                         }
                         tc_commit(smem_addr(&sm.s_full[sb]));
                         TRACE(2, g);
@@ -287,29 +326,28 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 }
             } else {
                 constexpr uint32_t idesc = make_idesc_bf16(ROWS, 256, true);
+                constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(1024);
+                const uint32_t p_lo = sw128_desc_lo(smem_addr(sm.data + VA_P), 16);
+                const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), BOX_BYTES);
                 for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         for (int h = 0; h < 2; ++h) {
                             const uint32_t pb = (g & 1) * 2 + h, pph = (g >> 1) & 1;
                             wt.wait<true>(&sm.p_full[pb], pph, 104);
-                            TRACE(9, 2 * g + h);
                             wt.wait<false>(&sm.corr_done[pb], pph, 105);
-                            fence_proxy_async();
-                            tc_fence_after();
-                            TRACE(10, 2 * g + h);
-                            const uint32_t pbase = smem_addr(sm.data + VA_P + pb * P_SUB_BYTES);
+                            const uint32_t a_lo = p_lo + pb * (P_SUB_BYTES >> 4);
+#pragma unroll
                             for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
                                 wt.wait<false>(&sm.kv_full[slot], (ks / NVS) & 1, 103);
+                                if (nh == 0) fence_proxy_async_smem();
                                 tc_fence_after();
-                                const uint32_t vbase = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
+                                const uint32_t b_lo = vring_lo + slot * (V_SLOT_BYTES >> 4);
 #pragma unroll
-                                for (int kt = 0; kt < PAGE / 16; ++kt) {
-                                    const uint64_t adesc = make_sw128_desc(pbase + kt * 32, 16, 1024);
-                                    const uint64_t bdesc = make_sw128_desc(vbase + kt * 2048, BOX_BYTES, 1024);
-                                    mma_ss(tmem + nh * 256, adesc, bdesc, idesc, (i > 0 || h > 0 || kt > 0) ? 1u : 0u);
-                                }
+                                for (int kt = 0; kt < PAGE / 16; ++kt)
+                                    mma_ss_lohi(tmem + nh * 256, a_lo + kt * 2, hi_a, b_lo + kt * (2048 >> 4), hi_b, idesc,
+                                                (i > 0 || h > 0 || kt > 0) ? 1u : 0u);
                                 tc_commit(smem_addr(&sm.kv_empty[slot]));
                             }
                             tc_commit(smem_addr(&sm.pv_done[pb]));
@@ -318,9 +356,51 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 }
             }
         }
-    } else if (warp == 2) {
+    } else if (warp == 2 || warp == 3) {
+#ifdef MLA_TRACE_KLAND
+        if (cta_rank == 0 && lane == 0) {      // debug: when does the data of K chunk 0 / 8 of every tile land
+            uint32_t ks = 0;
+            for (Walker wk(p, part); wk.valid(); wk.next()) {
+                const Work w = wk.get();
+                for (int i = 0; i < w.ntiles; ++i)
+                    for (int j = 0; j < 9; ++j, ++ks) {
+                        wt.wait<false>(&sm.kv_full[ks % NKS], (ks / NKS) & 1, 99);
+                        if (j == 0) TRACE(9, 2 * (ks / 9));
+                        if (j == 8) TRACE(9, 2 * (ks / 9) + 1);
+                    }
+            }
+        }
+#endif
+        // ---------------- score CTA: push finished P pages (and, with page 0, the rescale factors) to the value CTA
+        if (cta_rank == 0 && lane == 0) {
+            const int half = warp - 2;
+            uint32_t g = 0;
+            const uint32_t src_p = smem_addr(sm.data + SC_STAGE + half * 4 * 4096);
+            const uint32_t src_side = smem_addr(sm.data + SC_SIDE);
+            const uint32_t remote_p = map_to_cta(smem_addr(sm.data + VA_P), 1);
+            const uint32_t remote_side = map_to_cta(smem_addr(&sm.side[0][0][0]), 1);
+            uint32_t remote_p_full[NPB];
+            for (int i = 0; i < NPB; ++i) remote_p_full[i] = map_to_cta(smem_addr(&sm.p_full[i]), 1);
+            for (Walker wk(p, part); wk.valid(); wk.next()) {
+                const Work w = wk.get();
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
+                    const uint32_t pb = (g & 1) * 2 + half;
+                    wt.wait<false>(&sm.stage_full[half], g & 1, 9);
+                    wt.wait<true>(&sm.p_empty[pb], ((g >> 1) & 1) ^ 1, 6);   // that P buffer of the value CTA has been consumed
+                    if (half == 0) { TRACE(5, g); TRACE_CLOCK(9, g); }
+                    // p_full[pb] is armed (arrival + expected bytes) by the value CTA itself: a remote arrive with
+                    // release semantics costs over a microsecond, the copies below only count bytes.
+                    if (half == 0) TRACE_CLOCK(10, g);
+                    bulk_copy_to_cluster(remote_p + pb * P_SUB_BYTES, src_p, P_SUB_BYTES, remote_p_full[pb]);
+                    if (half == 0) TRACE_CLOCK(11, g);
+                    if (half == 0)
+                        bulk_copy_to_cluster(remote_side + (g & 1) * 4 * SIDE_BYTES, src_side, 4 * SIDE_BYTES, remote_p_full[pb]);
+                    if (half == 0) { TRACE_CLOCK(12, g); TRACE(6, g); }
+                }
+            }
+        }
         // ---------------- value CTA: tell the score CTA when a P buffer has been consumed ------------------
-        if (cta_rank == 1 && lane == 0) {
+        if (cta_rank == 1 && warp == 2 && lane == 0) {
             uint32_t g = 0;
             uint32_t remote_p_empty[NPB];
             for (int i = 0; i < NPB; ++i) remote_p_empty[i] = map_to_cta(smem_addr(&sm.p_empty[i]), 0);
@@ -330,8 +410,10 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t pb = (g & 1) * 2 + h;
                         wt.wait<false>(&sm.pv_done[pb], (g >> 1) & 1, 106);
-                        TRACE(11, 2 * g + h);
-                        mbar_arrive_remote(remote_p_empty[pb]);
+                        // arm the buffer's barrier for its next use, then let the score CTA refill it
+                        if (wt.aborted) continue;            // never arm a barrier whose previous phase may be open
+                        mbar_arrive_expect_tx(smem_addr(&sm.p_full[pb]), P_SUB_BYTES + (h == 0 ? 4 * SIDE_BYTES : 0));
+                        mbar_arrive_remote_relaxed(remote_p_empty[pb]);
                     }
                 }
             }
@@ -352,10 +434,6 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             uint8_t* stage = sm.data + SC_STAGE + (half * 4 + wq) * 4096;
             float* side_src = reinterpret_cast<float*>(sm.data + SC_SIDE + wq * SIDE_BYTES);
             float* xmax = reinterpret_cast<float*>(sm.data + SC_XMAX);
-            const uint32_t remote_p = map_to_cta(smem_addr(sm.data + VA_P), 1) + wq * 4096;
-            const uint32_t remote_side = map_to_cta(smem_addr(&sm.side[0][wq][0]), 1);
-            uint32_t remote_p_full[NPB];
-            for (int i = 0; i < NPB; ++i) remote_p_full[i] = map_to_cta(smem_addr(&sm.p_full[i]), 1);
             const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[half][r]), 1);
             const uint32_t remote_fin_m = map_to_cta(smem_addr(&sm.fin_m[r]), 1);
             const uint32_t remote_fin_full = map_to_cta(smem_addr(&sm.fin_full), 1);
@@ -416,13 +494,18 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
                     const int nvalid = limit - (w.blk_begin + 2 * i + half) * PAGE;   // columns [0, nvalid) are visible
-                    float mx = -INFINITY;
+                    if (nvalid < PAGE) {
 #pragma unroll
-                    for (int c = 0; c < 64; ++c) {
-                        const float v = c < nvalid ? __uint_as_float(s[c]) : -INFINITY;
-                        s[c] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
+                        for (int c = 0; c < 64; ++c)
+                            if (c >= nvalid) s[c] = 0xff800000u;          // -inf
                     }
+                    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                    for (int c = 0; c < 64; c += 2) {
+                        mx0 = fmaxf(mx0, __uint_as_float(s[c]));
+                        mx1 = fmaxf(mx1, __uint_as_float(s[c + 1]));
+                    }
+                    float mx = fmaxf(mx0, mx1);
                     // the row maximum over both pages of the tile
                     xmax[((g & 1) * 2 + half) * ROWS + r] = mx;
                     named_bar_sync(1, 256);
@@ -464,19 +547,8 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                             if (lane == 0) reinterpret_cast<uint32_t*>(side_src)[32] = any_resc ? 1u : 0u;
                         }
                     }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) {
-                        const uint32_t pb = (g & 1) * 2 + half;
-                        wt.wait<true>(&sm.p_empty[pb], ph ^ 1, 6);    // that P buffer of the value CTA has been consumed
-                        if (threadIdx.x == 128) TRACE(5, g);
-                        mbar_arrive_expect_tx_remote(remote_p_full[pb], 4096 + (half == 0 ? SIDE_BYTES : 0));
-                        bulk_copy_to_cluster(remote_p + pb * P_SUB_BYTES, smem_addr(stage), 4096, remote_p_full[pb]);
-                        if (half == 0)
-                            bulk_copy_to_cluster(remote_side + (g & 1) * 4 * SIDE_BYTES, smem_addr(side_src), SIDE_BYTES, remote_p_full[pb]);
-                        if (threadIdx.x == 128) TRACE(6, g);
-                    }
-                    __syncwarp();
+                    fence_proxy_async_smem();                          // staging is read by the bulk-copy engine
+                    mbar_arrive(smem_addr(&sm.stage_full[half]));      // the sender warp pushes it to the value CTA
                 }
                 // final statistics of this request for the epilogue in the value CTA
                 wt.wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
@@ -497,8 +569,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                         const uint32_t pb = (g & 1) * 2 + h, ph = (g >> 1) & 1;
                         wt.wait<true>(&sm.p_full[pb], ph, 107);
                         if (threadIdx.x == 128) {
-                            TRACE(12, 2 * g + h);
-                            mbar_arrive_remote(h ? remote_stage_free1 : remote_stage_free0);   // the copy has landed
+                            mbar_arrive_remote_relaxed(h ? remote_stage_free1 : remote_stage_free0);   // the copy has landed
                         }
                         if (h == 0 && i > 0) {
                             const float* side = reinterpret_cast<const float*>(&sm.side[g & 1][wq][0]);
@@ -536,7 +607,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                                     *reinterpret_cast<uint4*>(vst + box * BOX_BYTES + rr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
                                 }
                             }
-                            fence_proxy_async();
+                            fence_proxy_async_smem();
                         }
                         tc_fence_before();
                         mbar_arrive(smem_addr(&sm.corr_done[pb]));
