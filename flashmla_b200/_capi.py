@@ -15,6 +15,7 @@ MLA_MODE_DENSE_DECODE = 0
 MLA_MODE_SPARSE_DECODE = 1
 
 IMPL_AUTO, IMPL_PORTABLE, IMPL_TCGEN05 = 0, 1, 2
+NOALLOC_MAX_ROWS = 16384
 
 
 class SchedMetaArgs(Structure):
@@ -96,6 +97,7 @@ SYMBOLS = {
     "mla_sparse_decode_fwd": (c_int, [POINTER(SparseDecodeArgs)]),
     "mla_combine": (c_int, [POINTER(CombineArgs)]),
     "mla_sparse_prefill_fwd": (c_int, [POINTER(SparsePrefillArgs)]),
+    "mla_dense_decode_noalloc": (c_int, [POINTER(DenseDecodeArgs)]),
 }
 
 _lib = None

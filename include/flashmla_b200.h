@@ -211,6 +211,19 @@ typedef struct {
 } mla_sparse_prefill_args_t;
 int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* args);
 
+/* Dense decode INCLUDING the combine step, for callers that cannot allocate device memory (engines whose
+ * decode loop runs on a memory plan fixed at start-up, where a cudaMalloc would stall the device or fail;
+ * host runtimes that bind this ABI without a device allocator).  Same arguments as mla_dense_decode_fwd, but
+ * args->lse_accum and args->o_accum are ignored: the split-KV scratch is a fixed array inside the library,
+ * about 32 MiB per GPU that loads it, held until the process exits.  Limit: (b + num_sm_parts) * s_q * h_q
+ * must not exceed MLA_NOALLOC_MAX_ROWS, otherwise MLA_ERR_INVALID_ARG is returned.  The first call on each
+ * device looks up the array's device address (make that call with the device current and before any stream
+ * capture).  All calls on a GPU share the array: calls that may overlap on the GPU race and must be
+ * serialised by the caller.  Nothing in the array needs clearing between calls.  Calls no allocation routine.
+ * This entry point has no counterpart in the reference. */
+#define MLA_NOALLOC_MAX_ROWS 16384
+int mla_dense_decode_noalloc(const mla_dense_decode_args_t* args);
+
 #ifdef __cplusplus
 }
 #endif
