@@ -156,7 +156,12 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* a) {
     MLA_CHECK_ARG(is_aligned16(a->kv) && a->kv_stride_s % 8 == 0,
                   "mla_sparse_prefill_fwd: kv must be 16-byte aligned with a row stride that is a multiple of 8 elements");
     MLA_CHECK_ARG(is_aligned16(a->out), "mla_sparse_prefill_fwd: out must be 16-byte aligned");
-    if (a->impl == 2) return set_error(MLA_ERR_UNSUPPORTED, "mla_sparse_prefill_fwd: no tcgen05 kernel for this shape");
+    if (a->impl == 2) {
+        if (!sparse_prefill_sm100_supports(*a))
+            return set_error(MLA_ERR_UNSUPPORTED, "mla_sparse_prefill_fwd: the tcgen05 kernel does not support this shape");
+        return launch_sparse_prefill_sm100(*a);
+    }
+    if (a->impl == 0 && sparse_prefill_sm100_supports(*a)) return launch_sparse_prefill_sm100(*a);
     return launch_sparse_prefill_portable(*a);
 }
 

@@ -77,7 +77,8 @@ constexpr int DATA_BYTES = VA_END > SC_END ? VA_END : SC_END;
 struct Smem {
     uint8_t data[DATA_BYTES];
     uint8_t side[2][4][SIDE_BYTES];      // value CTA: factors + flag received with the first page of tile parity 0 / 1
-    float fin_l[2][ROWS], fin_m[ROWS];   // value CTA: final row sums (one per softmax warpgroup) / running maximum
+    float fin_l[ROWS], fin_m[ROWS];      // value CTA: final row sum / running maximum of the request
+    float fin_mt[ROWS];                  // value CTA: true row maximum (the running maximum may lag it by up to 2^6)
     uint64_t kv_full[NRING], kv_empty[NRING];     // K groups (score CTA) / V slots (value CTA)
     uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
@@ -98,14 +99,27 @@ struct Params {
     float* lse_accum; float* o_accum;
     int* status;
     int row_blocks;
+    // token-sparse prefill: one "request" is one query token, its keys are gathered by index
+    const int* indices; int64_t idx_ss; int topk; const int* topk_len; int s_kv;
+    const float* attn_sink; float* max_logits;
 };
+
+enum { MODE_DENSE = 0, MODE_PREFILL = 1 };
+constexpr int SC_MASK = SC_END;          // score CTA, prefill: validity bits of the last 4 tiles, [4][4] words
+constexpr int SC_LSUM = SC_MASK + 64;    // score CTA: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
+static_assert(SC_LSUM + ROWS * 4 <= DATA_BYTES, "score CTA scratch must fit");
 
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
     int req, blk_begin, blk_end, ntiles, seqlen, is_split, slot;
 };
 
-struct Walker {
+template <int MODE>
+struct Walker;
+
+// dense decode: the requests and block range of one SM partition, from the tile-scheduler metadata
+template <>
+struct Walker<MODE_DENSE> {
     mla_sched_meta_t m;
     const Params& p;
     int req;
@@ -124,6 +138,28 @@ struct Walker {
         return w;
     }
     __device__ void next() { ++req; }
+};
+
+// sparse prefill: CTA pair `part` takes query tokens part, part + gridDim.z, ... ; "seqlen" is the number of
+// top-k positions that may be valid
+template <>
+struct Walker<MODE_PREFILL> {
+    const Params& p;
+    int req;
+    __device__ Walker(const Params& p_, int part) : p(p_), req(part) {}
+    __device__ bool valid() const { return req < p.b; }
+    __device__ Work get() const {
+        Work w;
+        w.req = req;
+        w.seqlen = p.topk_len ? min(max(p.topk_len[req], 0), p.topk) : p.topk;
+        w.blk_begin = 0;
+        w.blk_end = (w.seqlen + PAGE - 1) / PAGE;
+        w.ntiles = (w.blk_end + 1) / 2;
+        w.is_split = 0;
+        w.slot = 0;
+        return w;
+    }
+    __device__ void next() { req += gridDim.z; }
 };
 
 // Bounded wait helper: after the first expiry the thread stops waiting altogether.
@@ -171,8 +207,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return r;
 }
 
+template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
-dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
+attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
+    using WalkerT = Walker<MODE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();          // 0 = score CTA, 1 = value CTA
@@ -202,7 +240,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
         }
         mbar_init(smem_addr(&sm.q_ready), 256);
         mbar_init(smem_addr(&sm.fin_empty), 128);
-        mbar_init(smem_addr(&sm.fin_full), 256);
+        mbar_init(smem_addr(&sm.fin_full), 128);
         sm.aborted = 0;
         // first use of every P buffer: its arrival and expected byte count are armed here (matters in the value CTA)
         for (int i = 0; i < NPB; ++i)
@@ -222,9 +260,76 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
     // =====================================================================================================
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ---------------------------------------------------------
-        if (lane == 0) {
+        if (MODE == MODE_PREFILL) {
+            // Gather by index: lane l fetches rows 4l..4l+3 of a tile (score CTA) or of a page (value CTA) with one
+            // gather4 per 64-dim chunk.  Invalid entries (index outside [0, s_kv) or position beyond topk_length)
+            // use a row coordinate outside the tensor, which TMA fills with zeros; the score CTA also records a
+            // validity bit per token for the softmax.
+            uint32_t ks = 0, g = 0;
+            uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+                const Work w = wk.get();
+                const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
+                    if (cta_rank == 0) {
+                        int rows[4];
+                        uint32_t bal[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int pos = i * 128 + lane * 4 + k;
+                            const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                            const bool ok = id >= 0 && id < p.s_kv;
+                            rows[k] = ok ? id : p.s_kv;
+                            bal[k] = __ballot_sync(0xffffffffu, ok);
+                        }
+                        if (lane == 0) {
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) kmask[(g & 3) * 4 + k] = bal[k];
+                        }
+                        for (int grp = 0; grp < 3; ++grp, ++ks) {
+                            const uint32_t bar = smem_addr(&sm.kv_full[grp]);
+                            if (lane == 0) {
+                                wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 1);
+                                mbar_arrive_expect_tx(bar, K_GROUP_BYTES);      // releases the mask words too
+                            }
+                            __syncwarp();
+                            const uint32_t dst = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES) + lane * 512;
+#pragma unroll
+                            for (int c = 0; c < 3; ++c)
+                                tma_gather4_2d(dst + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, rows[0], rows[1], rows[2], rows[3]);
+                        }
+                    } else {
+                        for (int h = 0; h < 2; ++h) {
+                            int rows[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const int pos = i * 128 + h * 64 + (lane & 15) * 4 + k;
+                                const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                                rows[k] = (id >= 0 && id < p.s_kv) ? id : p.s_kv;
+                            }
+                            for (int nh = 0; nh < 2; ++nh, ++ks) {
+                                const uint32_t slot = ks % NVS;
+                                const uint32_t bar = smem_addr(&sm.kv_full[slot]);
+                                if (lane == 0) {
+                                    wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
+                                    mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
+                                }
+                                __syncwarp();
+                                // lanes 0-15 fill boxes 0 and 1 of the slot, lanes 16-31 boxes 2 and 3
+                                const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES) + (lane & 15) * 512;
+#pragma unroll
+                                for (int bx = 0; bx < 2; ++bx) {
+                                    const int box = (lane >> 4) * 2 + bx;
+                                    tma_gather4_2d(dst + box * BOX_BYTES, &kmap, bar, (nh * 4 + box) * 64, rows[0], rows[1], rows[2], rows[3]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
             uint32_t ks = 0;                               // ring slot counter (K chunks or V half-pages)
-            for (Walker wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
                 // page ids are fetched one tile ahead so the block-table latency stays off the TMA issue path
@@ -282,7 +387,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 const uint32_t kring_lo = sw128_desc_lo(smem_addr(sm.data + SC_KRING), 16);
                 const uint32_t kv_empty0 = smem_addr(&sm.kv_empty[0]);
                 const uint32_t kv_full0 = smem_addr(&sm.kv_full[0]);
-                for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
+                for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     wt.wait<false>(&sm.q_ready, nreq & 1, 2);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
@@ -329,7 +434,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(1024);
                 const uint32_t p_lo = sw128_desc_lo(smem_addr(sm.data + VA_P), 16);
                 const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), BOX_BYTES);
-                for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
+                for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         for (int h = 0; h < 2; ++h) {
@@ -360,7 +465,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
 #ifdef MLA_TRACE_KLAND
         if (cta_rank == 0 && lane == 0) {      // debug: when does the data of K chunk 0 / 8 of every tile land
             uint32_t ks = 0;
-            for (Walker wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 for (int i = 0; i < w.ntiles; ++i)
                     for (int j = 0; j < 9; ++j, ++ks) {
@@ -381,7 +486,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             const uint32_t remote_side = map_to_cta(smem_addr(&sm.side[0][0][0]), 1);
             uint32_t remote_p_full[NPB];
             for (int i = 0; i < NPB; ++i) remote_p_full[i] = map_to_cta(smem_addr(&sm.p_full[i]), 1);
-            for (Walker wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t pb = (g & 1) * 2 + half;
@@ -404,7 +509,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             uint32_t g = 0;
             uint32_t remote_p_empty[NPB];
             for (int i = 0; i < NPB; ++i) remote_p_empty[i] = map_to_cta(smem_addr(&sm.p_empty[i]), 0);
-            for (Walker wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     for (int h = 0; h < 2; ++h) {
@@ -434,16 +539,19 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             uint8_t* stage = sm.data + SC_STAGE + (half * 4 + wq) * 4096;
             float* side_src = reinterpret_cast<float*>(sm.data + SC_SIDE + wq * SIDE_BYTES);
             float* xmax = reinterpret_cast<float*>(sm.data + SC_XMAX);
-            const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[half][r]), 1);
+            const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[r]), 1);
             const uint32_t remote_fin_m = map_to_cta(smem_addr(&sm.fin_m[r]), 1);
+            const uint32_t remote_fin_mt = map_to_cta(smem_addr(&sm.fin_mt[r]), 1);
             const uint32_t remote_fin_full = map_to_cta(smem_addr(&sm.fin_full), 1);
-            for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
                 // ---- Q row -> A operand: chunks 0..6 to tensor memory (2 bf16 per 32-bit column), chunks 7, 8 to shared
                 // memory (K-major, 128-byte swizzle).  Warpgroup 0 takes chunks 0-3 and 7, warpgroup 1 chunks 4-6 and 8.
                 // Every MMA that read the previous request's Q has completed: this thread saw s_full of its last tile.
                 {
-                    const __nv_bfloat16* qrow = p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
+                    const __nv_bfloat16* qrow = MODE == MODE_PREFILL
+                        ? p.q + (int64_t)w.req * p.q_ss + (int64_t)hd * p.q_sh
+                        : p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
                     const int c_begin = half ? 4 : 0, c_end = half ? 7 : 4, c_smem = half ? 8 : 7;
 #pragma unroll 1
                     for (int c = c_begin; c <= c_end; ++c) {
@@ -476,7 +584,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 }
                 // first key position this row must NOT see (causal limit, and the end of this partition's range)
                 const int limit = min(p.causal ? w.seqlen - (p.s_q - 1 - t) : w.seqlen, w.blk_end * PAGE);
-                float m_run = -INFINITY, l_run = 0.f;
+                float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t sb = g & 1, ph = (g >> 1) & 1;
                     wt.wait<false>(&sm.s_full[sb], ph, 5);
@@ -493,11 +601,25 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     tc_fence_before();
                     mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
-                    const int nvalid = limit - (w.blk_begin + 2 * i + half) * PAGE;   // columns [0, nvalid) are visible
-                    if (nvalid < PAGE) {
+                    if (MODE == MODE_PREFILL) {
+                        // validity bits of the gathered tokens: token 4l+k of the tile is bit l of word k
+                        const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + SC_MASK) + (g & 3) * 4;
+                        const uint32_t m0 = km[0] >> (half * 16), m1 = km[1] >> (half * 16);
+                        const uint32_t m2 = km[2] >> (half * 16), m3 = km[3] >> (half * 16);
+                        if (((m0 & m1 & m2 & m3) & 0xffffu) != 0xffffu) {
 #pragma unroll
-                        for (int c = 0; c < 64; ++c)
-                            if (c >= nvalid) s[c] = 0xff800000u;          // -inf
+                            for (int c = 0; c < 64; ++c) {
+                                const uint32_t word = (c & 3) == 0 ? m0 : ((c & 3) == 1 ? m1 : ((c & 3) == 2 ? m2 : m3));
+                                if (!((word >> (c >> 2)) & 1u)) s[c] = 0xff800000u;      // -inf
+                            }
+                        }
+                    } else {
+                        const int nvalid = limit - (w.blk_begin + 2 * i + half) * PAGE;   // columns [0, nvalid) are visible
+                        if (nvalid < PAGE) {
+#pragma unroll
+                            for (int c = 0; c < 64; ++c)
+                                if (c >= nvalid) s[c] = 0xff800000u;          // -inf
+                        }
                     }
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -511,6 +633,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     named_bar_sync(1, 256);
                     mx = fmaxf(mx, xmax[((g & 1) * 2 + (half ^ 1)) * ROWS + r]);
                     mx *= p.scale_log2;                                // scale > 0: max commutes with scaling
+                    m_true = fmaxf(m_true, mx);
                     float factor = 1.f;
                     bool resc = false;
                     if (i == 0) {
@@ -550,11 +673,22 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                     fence_proxy_async_smem();                          // staging is read by the bulk-copy engine
                     mbar_arrive(smem_addr(&sm.stage_full[half]));      // the sender warp pushes it to the value CTA
                 }
-                // final statistics of this request for the epilogue in the value CTA
-                wt.wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
-                st_cluster_f32(remote_fin_l, l_run);
-                if (half == 0) st_cluster_f32(remote_fin_m, m_run);
-                mbar_arrive_remote(remote_fin_full);
+                // final statistics of this request for the epilogue in the value CTA: warpgroup 1 hands its row sums to
+                // warpgroup 0, which sends sum, running maximum and true maximum
+                {
+                    float* lsum = reinterpret_cast<float*>(sm.data + SC_LSUM);
+                    if (half == 1) lsum[r] = l_run;
+                    named_bar_sync(1, 256);
+                    if (half == 0) l_run += lsum[r];
+                    named_bar_sync(1, 256);
+                }
+                if (half == 0) {
+                    wt.wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
+                    st_cluster_f32(remote_fin_l, l_run);
+                    st_cluster_f32(remote_fin_m, m_run);
+                    st_cluster_f32(remote_fin_mt, m_true);
+                    mbar_arrive_remote(remote_fin_full);
+                }
             }
         } else if (warp < 8) {
             // ---------------- correction / epilogue warpgroup of the value CTA ---------------------------------
@@ -562,7 +696,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
             const uint32_t remote_stage_free0 = map_to_cta(smem_addr(&sm.stage_free[0]), 0);
             const uint32_t remote_stage_free1 = map_to_cta(smem_addr(&sm.stage_free[1]), 0);
             uint32_t vs = 0;                                          // V ring slot counter
-            for (Walker wk(p, part); wk.valid(); wk.next(), ++nreq) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     for (int h = 0; h < 2; ++h, vs += 2) {
@@ -595,7 +729,7 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                         // their probabilities are zero, so their V rows are zeroed to keep 0 * NaN out of O.
                         const int blk = w.blk_begin + 2 * i + h;
                         const int nvalid = w.seqlen - blk * PAGE;
-                        if (blk < w.blk_end && nvalid < PAGE) {
+                        if (MODE == MODE_DENSE && blk < w.blk_end && nvalid < PAGE) {
                             const int first = max(nvalid, 0);
                             for (int nh = 0; nh < 2; ++nh) {
                                 const uint32_t slot = (vs + nh) % NVS;
@@ -618,11 +752,15 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                 if (has_tiles) wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 110);
                 wt.wait<true>(&sm.fin_full, nreq & 1, 111);
                 tc_fence_after();
-                const float L = sm.fin_l[0][r] + sm.fin_l[1][r], M = sm.fin_m[r];
+                const float L = sm.fin_l[r], M = sm.fin_m[r];
                 const bool empty = !(L > 0.f) || !has_tiles;          // also catches NaN
-                const float scale = empty ? 0.f : 1.f / L;
+                float scale = empty ? 0.f : 1.f / L;
+                if (MODE == MODE_PREFILL && p.attn_sink && !empty && row_ok)
+                    scale = 1.f / (L + exp2f(p.attn_sink[hd] * kLog2e - M));
                 if (!w.is_split) {
-                    __nv_bfloat16* orow = p.out + (int64_t)w.req * p.o_sb + (int64_t)t * p.o_ss + (int64_t)hd * p.o_sh;
+                    __nv_bfloat16* orow = MODE == MODE_PREFILL
+                        ? p.out + ((int64_t)w.req * p.h_q + hd) * D_V
+                        : p.out + (int64_t)w.req * p.o_sb + (int64_t)t * p.o_ss + (int64_t)hd * p.o_sh;
 #pragma unroll 1
                     for (int c = 0; c < D_V / 32; ++c) {
                         uint32_t v[32];
@@ -639,7 +777,15 @@ dense_decode_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params
                             }
                         }
                     }
-                    if (row_ok) p.lse[w.req * p.l_sb + t * p.l_ss + hd * p.l_sh] = empty ? INFINITY : (log2f(L) + M) * kLn2;
+                    if (row_ok) {
+                        const float lse_nat = empty ? INFINITY : (log2f(L) + M) * kLn2;
+                        if (MODE == MODE_PREFILL) {
+                            p.lse[(int64_t)w.req * p.h_q + hd] = lse_nat;
+                            p.max_logits[(int64_t)w.req * p.h_q + hd] = empty ? -INFINITY : sm.fin_mt[r] * kLn2;
+                        } else {
+                            p.lse[w.req * p.l_sb + t * p.l_ss + hd * p.l_sh] = lse_nat;
+                        }
+                    }
                 } else {
                     const int64_t arow = ((int64_t)w.slot * p.s_q + t) * p.h_q + hd;
                     float* orow = p.o_accum + arow * D_V;
@@ -751,11 +897,62 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     int dev = 0;
     MLA_CHECK_CUDA(cudaGetDevice(&dev));
     if (dev >= 64 || !configured[dev]) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(dense_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
         if (dev < 64) configured[dev] = true;
     }
     dim3 grid(2, p.row_blocks * a.h_kv, a.num_sm_parts);
-    dense_decode_sm100_kernel<<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    MLA_CHECK_CUDA(cudaGetLastError());
+    return MLA_OK;
+}
+
+bool sparse_prefill_sm100_supports(const mla_sparse_prefill_args_t& a) {
+    if (a.d_qk != 576 || a.d_v != 512 || a.h_kv != 1) return false;
+    if (a.kv_stride_s <= 0 || a.kv_stride_s % 8 || a.kv_stride_s >= ((int64_t)1 << 39)) return false;
+    if (!(a.sm_scale > 0.f)) return false;
+    if (a.h_q > 128 * 65535) return false;
+    return true;
+}
+
+int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
+    using namespace sm100;
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    // kv as a 2-D tensor (576, s_kv); rows are fetched four at a time by index (gather4), 64 columns per box
+    CUtensorMap kmap;
+    cuuint64_t dims[2] = {(cuuint64_t)D_QK, (cuuint64_t)a.s_kv};
+    cuuint64_t strides[1] = {(cuuint64_t)a.kv_stride_s * 2};
+    cuuint32_t box[2] = {64, 1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.kv), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+
+    Params p = {};
+    p.b = a.s_q; p.s_q = 1; p.h_q = a.h_q; p.h_kv = 1; p.g = a.h_q; p.rows = a.h_q;
+    p.causal = 0;
+    p.scale_log2 = a.sm_scale * kLog2e;
+    p.q = (const __nv_bfloat16*)a.q; p.q_ss = a.q_stride_s; p.q_sh = a.q_stride_h;
+    p.out = (__nv_bfloat16*)a.out; p.lse = a.lse; p.max_logits = a.max_logits;
+    p.attn_sink = a.attn_sink;
+    p.indices = a.indices; p.idx_ss = a.indices_stride_s; p.topk = a.topk; p.topk_len = a.topk_length; p.s_kv = a.s_kv;
+    p.status = a.status;
+    p.row_blocks = (p.rows + ROWS - 1) / ROWS;
+
+    int dev = 0;
+    MLA_CHECK_CUDA(cudaGetDevice(&dev));
+    static bool configured[64] = {};
+    if (dev >= 64 || !configured[dev]) {
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        if (dev < 64) configured[dev] = true;
+    }
+    const int sms = device_num_sms(dev);
+    int pairs = sms / 2 / p.row_blocks;
+    if (pairs < 1) pairs = 1;
+    if (pairs > a.s_q) pairs = a.s_q;
+    dim3 grid(2, p.row_blocks, pairs);
+    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

@@ -116,6 +116,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
         ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
 
+// Row gather: four rows (given by their row coordinates) of a 2-D tensor, `box` columns starting at column c0, land
+// consecutively in shared memory (row coordinates outside the tensor read the fill value, zero).
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int r0, int r1, int r2, int r3) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+
 // Bulk copy from this CTA's shared memory into another CTA of the cluster; the bytes are counted on a
 // barrier of the destination CTA.  Addresses and size are multiples of 16 bytes.
 __device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {

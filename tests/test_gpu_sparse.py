@@ -22,6 +22,7 @@ def _decode(q, kv, indices, sm_scale, attn_sink=None, topk_length=None, extra_kv
     out, lse = fm.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, sm_scale, False, True, indices, attn_sink,
                                          extra_kv, extra_indices, topk_length, extra_topk_length)
     torch.cuda.synchronize()
+    fm.check_status()
     return out, lse
 
 
@@ -104,6 +105,7 @@ def _prefill(q, kv, indices, sm_scale, attn_sink=None, topk_length=None):
     import flashmla_b200 as fm
     out, mx, lse = fm.flash_mla_sparse_fwd(q, kv, indices, sm_scale, 512, attn_sink, topk_length)
     torch.cuda.synchronize()
+    fm.check_status()
     return out, mx, lse
 
 
