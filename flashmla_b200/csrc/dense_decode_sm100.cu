@@ -105,6 +105,10 @@ struct Params {
 };
 
 enum { MODE_DENSE = 0, MODE_PREFILL = 1 };
+#ifndef MLA_GATHER_LANES
+#define MLA_GATHER_LANES 8
+#endif
+constexpr int GATHER_LANES = MLA_GATHER_LANES;     // lanes of the producer warp that issue row gathers
 constexpr int SC_MASK = SC_END;          // score CTA, prefill: validity bits of the last 4 tiles, [4][4] words
 constexpr int SC_LSUM = SC_MASK + 64;    // score CTA: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
 static_assert(SC_LSUM + ROWS * 4 <= DATA_BYTES, "score CTA scratch must fit");
@@ -265,6 +269,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
             // gather4 per 64-dim chunk.  Invalid entries (index outside [0, s_kv) or position beyond topk_length)
             // use a row coordinate outside the tensor, which TMA fills with zeros; the score CTA also records a
             // validity bit per token for the softmax.
+            const uint64_t keep = l2_policy_evict_last();      // the gathered KV rows are re-read by every query token
             uint32_t ks = 0, g = 0;
             uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -293,10 +298,19 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                 mbar_arrive_expect_tx(bar, K_GROUP_BYTES);      // releases the mask words too
                             }
                             __syncwarp();
-                            const uint32_t dst = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES) + lane * 512;
+                            // GATHER_LANES lanes issue; lane l takes row groups l, l + GATHER_LANES, ... (rows come by shuffle)
+                            const uint32_t dst0 = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES);
 #pragma unroll
-                            for (int c = 0; c < 3; ++c)
-                                tma_gather4_2d(dst + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, rows[0], rows[1], rows[2], rows[3]);
+                            for (int rg0 = 0; rg0 < 32; rg0 += GATHER_LANES) {
+                                const int src = rg0 + (lane % GATHER_LANES);
+                                const int r0 = __shfl_sync(0xffffffffu, rows[0], src), r1 = __shfl_sync(0xffffffffu, rows[1], src);
+                                const int r2 = __shfl_sync(0xffffffffu, rows[2], src), r3 = __shfl_sync(0xffffffffu, rows[3], src);
+                                if (lane < GATHER_LANES) {
+#pragma unroll
+                                    for (int c = 0; c < 3; ++c)
+                                        tma_gather4_2d_hint(dst0 + src * 512 + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, r0, r1, r2, r3, keep);
+                                }
+                            }
                         }
                     } else {
                         for (int h = 0; h < 2; ++h) {
@@ -315,12 +329,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                     mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
                                 }
                                 __syncwarp();
-                                // lanes 0-15 fill boxes 0 and 1 of the slot, lanes 16-31 boxes 2 and 3
-                                const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES) + (lane & 15) * 512;
+                                const uint32_t dst0 = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
 #pragma unroll
-                                for (int bx = 0; bx < 2; ++bx) {
-                                    const int box = (lane >> 4) * 2 + bx;
-                                    tma_gather4_2d(dst + box * BOX_BYTES, &kmap, bar, (nh * 4 + box) * 64, rows[0], rows[1], rows[2], rows[3]);
+                                for (int rg0 = 0; rg0 < 16; rg0 += GATHER_LANES) {
+                                    const int src = rg0 + (lane % GATHER_LANES);
+                                    const int r0 = __shfl_sync(0xffffffffu, rows[0], src), r1 = __shfl_sync(0xffffffffu, rows[1], src);
+                                    const int r2 = __shfl_sync(0xffffffffu, rows[2], src), r3 = __shfl_sync(0xffffffffu, rows[3], src);
+                                    if (lane < GATHER_LANES) {
+#pragma unroll
+                                        for (int box = 0; box < 4; ++box)
+                                            tma_gather4_2d_hint(dst0 + box * BOX_BYTES + src * 512, &kmap, bar, (nh * 4 + box) * 64, r0, r1, r2, r3, keep);
+                                    }
                                 }
                             }
                         }

@@ -124,6 +124,30 @@ __device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* 
         ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
 
+// L2 eviction-priority policies for loads that should stay in (or get out of) L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_gather4_2d_hint(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int r0, int r1, int r2, int r3,
+                                                    uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+        ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "l"(policy) : "memory");
+}
+__device__ __forceinline__ uint4 ldg_evict_first(const uint4* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+    return v;
+}
+
 // Bulk copy from this CTA's shared memory into another CTA of the cluster; the bytes are counted on a
 // barrier of the destination CTA.  Addresses and size are multiples of 16 bytes.
 __device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {
