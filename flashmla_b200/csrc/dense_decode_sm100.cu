@@ -54,7 +54,8 @@ constexpr int P_SUB_BYTES = ROWS * PAGE * 2;  // P of one page: [128 rows][64 to
 constexpr int NPB = 4;                        // P buffers in the value CTA: (tile parity, page of the tile)
 constexpr int NRING = NKS > NVS ? NKS : NVS;
 constexpr int SIDE_BYTES = 144;               // per warp and tile: 32 rescale factors + flag (+ pad)
-constexpr int NTHREADS = 384;
+constexpr int NTHREADS = 384;                 // dense mode: control warpgroup + two softmax / correction warpgroups
+constexpr int NTHREADS_GATHER = 512;          // sparse modes: one more warpgroup that gathers KV rows by index
 constexpr long long WAIT_LIMIT = 2000000000LL;    // SM cycles (about one second)
 constexpr float RESCALE_THRESHOLD = 6.0f;         // log2 units
 
@@ -101,6 +102,7 @@ struct Params {
     int row_blocks;
     // token-sparse prefill: one "request" is one query token, its keys are gathered by index
     const int* indices; int64_t idx_ss; int topk; const int* topk_len; int s_kv;
+    const __nv_bfloat16* kv; int64_t kv_ss;
     const float* attn_sink; float* max_logits;
 };
 
@@ -212,7 +214,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int MODE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NTHREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
 attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     using WalkerT = Walker<MODE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -229,7 +231,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     }
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), 1); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
+        // a ring slot is filled by TMA (one arrive.expect_tx + bytes) in dense mode, by the 128 gather threads otherwise
+        for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), MODE == MODE_DENSE ? 1 : 128); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.s_full[i]), 1);
             mbar_init(smem_addr(&sm.s_empty[i]), 256);
@@ -250,7 +253,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
         for (int i = 0; i < NPB; ++i)
             mbar_arrive_expect_tx(smem_addr(&sm.p_full[i]), P_SUB_BYTES + ((i & 1) == 0 ? 4 * SIDE_BYTES : 0));
         fence_mbar_init();
-        prefetch_tensormap(&kmap);
+        if (MODE == MODE_DENSE) prefetch_tensormap(&kmap);
     }
     if (warp == 1) { tmem_alloc(smem_addr(&sm.tmem_base), 512); tmem_relinquish(); }
     tc_fence_before();
@@ -262,90 +265,14 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
 
     // =====================================================================================================
+    // In the sparse modes the CTA has 512 threads that start with 128 registers each; every warpgroup re-sizes its
+    // share as the first thing in its own branch (the compiler budgets registers per branch from this).
+    if (warp < 4) {
+    if (MODE != MODE_DENSE) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ---------------------------------------------------------
-        if (MODE == MODE_PREFILL) {
-            // Gather by index: lane l fetches rows 4l..4l+3 of a tile (score CTA) or of a page (value CTA) with one
-            // gather4 per 64-dim chunk.  Invalid entries (index outside [0, s_kv) or position beyond topk_length)
-            // use a row coordinate outside the tensor, which TMA fills with zeros; the score CTA also records a
-            // validity bit per token for the softmax.
-            const uint64_t keep = l2_policy_evict_last();      // the gathered KV rows are re-read by every query token
-            uint32_t ks = 0, g = 0;
-            uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
-            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
-                const Work w = wk.get();
-                const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
-                for (int i = 0; i < w.ntiles; ++i, ++g) {
-                    if (cta_rank == 0) {
-                        int rows[4];
-                        uint32_t bal[4];
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            const int pos = i * 128 + lane * 4 + k;
-                            const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
-                            const bool ok = id >= 0 && id < p.s_kv;
-                            rows[k] = ok ? id : p.s_kv;
-                            bal[k] = __ballot_sync(0xffffffffu, ok);
-                        }
-                        if (lane == 0) {
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) kmask[(g & 3) * 4 + k] = bal[k];
-                        }
-                        for (int grp = 0; grp < 3; ++grp, ++ks) {
-                            const uint32_t bar = smem_addr(&sm.kv_full[grp]);
-                            if (lane == 0) {
-                                wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 1);
-                                mbar_arrive_expect_tx(bar, K_GROUP_BYTES);      // releases the mask words too
-                            }
-                            __syncwarp();
-                            // GATHER_LANES lanes issue; lane l takes row groups l, l + GATHER_LANES, ... (rows come by shuffle)
-                            const uint32_t dst0 = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES);
-#pragma unroll
-                            for (int rg0 = 0; rg0 < 32; rg0 += GATHER_LANES) {
-                                const int src = rg0 + (lane % GATHER_LANES);
-                                const int r0 = __shfl_sync(0xffffffffu, rows[0], src), r1 = __shfl_sync(0xffffffffu, rows[1], src);
-                                const int r2 = __shfl_sync(0xffffffffu, rows[2], src), r3 = __shfl_sync(0xffffffffu, rows[3], src);
-                                if (lane < GATHER_LANES) {
-#pragma unroll
-                                    for (int c = 0; c < 3; ++c)
-                                        tma_gather4_2d_hint(dst0 + src * 512 + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, r0, r1, r2, r3, keep);
-                                }
-                            }
-                        }
-                    } else {
-                        for (int h = 0; h < 2; ++h) {
-                            int rows[4];
-#pragma unroll
-                            for (int k = 0; k < 4; ++k) {
-                                const int pos = i * 128 + h * 64 + (lane & 15) * 4 + k;
-                                const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
-                                rows[k] = (id >= 0 && id < p.s_kv) ? id : p.s_kv;
-                            }
-                            for (int nh = 0; nh < 2; ++nh, ++ks) {
-                                const uint32_t slot = ks % NVS;
-                                const uint32_t bar = smem_addr(&sm.kv_full[slot]);
-                                if (lane == 0) {
-                                    wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
-                                    mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
-                                }
-                                __syncwarp();
-                                const uint32_t dst0 = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
-#pragma unroll
-                                for (int rg0 = 0; rg0 < 16; rg0 += GATHER_LANES) {
-                                    const int src = rg0 + (lane % GATHER_LANES);
-                                    const int r0 = __shfl_sync(0xffffffffu, rows[0], src), r1 = __shfl_sync(0xffffffffu, rows[1], src);
-                                    const int r2 = __shfl_sync(0xffffffffu, rows[2], src), r3 = __shfl_sync(0xffffffffu, rows[3], src);
-                                    if (lane < GATHER_LANES) {
-#pragma unroll
-                                        for (int box = 0; box < 4; ++box)
-                                            tma_gather4_2d_hint(dst0 + box * BOX_BYTES + src * 512, &kmap, bar, (nh * 4 + box) * 64, r0, r1, r2, r3, keep);
-                                    }
-                                }
-                            }
-                        }
-                    }
-                }
-            }
+        if (MODE != MODE_DENSE) {
+            // sparse modes: the gather warpgroup fills the rings
         } else if (lane == 0) {
             uint32_t ks = 0;                               // ring slot counter (K chunks or V half-pages)
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -542,7 +469,72 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                 }
             }
         }
-    } else if (warp >= 4) {
+    }
+    } else if (MODE != MODE_DENSE && warp >= 12) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+        // ---------------- gather warpgroup (sparse modes): fills the K ring (score CTA) / V ring (value CTA) by index ----
+        // One thread per token: it reads its token's row from global memory (whole 32-byte sectors, many loads in
+        // flight) and writes it into the 128-byte-swizzled operand layout; invalid tokens get zeros.  The writes are
+        // generic-proxy stores, so each thread fences them for the tensor core's (async-proxy) reads before arriving.
+        const int tid = threadIdx.x - 384;
+        uint32_t ks = 0, g = 0;
+        uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
+        for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+            const Work w = wk.get();
+            const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
+            for (int i = 0; i < w.ntiles; ++i, ++g) {
+                if (cta_rank == 0) {
+                    const int pos = i * 128 + tid;
+                    const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                    const bool ok = id >= 0 && id < p.s_kv;
+                    const uint32_t bal = __ballot_sync(0xffffffffu, ok);
+                    if (lane == 0) kmask[(g & 3) * 4 + (warp - 12)] = bal;       // token w*32 + l of the tile is bit l of word w
+                    const uint4* src = reinterpret_cast<const uint4*>(p.kv + (int64_t)(ok ? id : 0) * p.kv_ss);
+                    uint8_t* rowdst = sm.data + SC_KRING + tid * 128;
+                    const int sw = tid & 7;
+                    for (int grp = 0; grp < 3; ++grp, ++ks) {
+                        wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {                          // 2 batches of 12 x 16 bytes
+                            uint4 v[12];
+#pragma unroll
+                            for (int k = 0; k < 12; ++k) v[k] = ok ? __ldg(src + grp * 24 + hb * 12 + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                            for (int k = 0; k < 12; ++k) {
+                                const int c16 = grp * 24 + hb * 12 + k, j = c16 >> 3, c = c16 & 7;
+                                *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = v[k];
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        mbar_arrive(smem_addr(&sm.kv_full[grp]));
+                    }
+                } else {
+                    const int tok = tid & 63, part2 = tid >> 6;                   // part2: boxes {0,1} or {2,3} of a slot
+                    const int sw = tok & 7;
+                    for (int h = 0; h < 2; ++h) {
+                        const int pos = i * 128 + h * 64 + tok;
+                        const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                        const bool ok = id >= 0 && id < p.s_kv;
+                        const uint4* src = reinterpret_cast<const uint4*>(p.kv + (int64_t)(ok ? id : 0) * p.kv_ss);
+                        for (int nh = 0; nh < 2; ++nh, ++ks) {
+                            const uint32_t slot = ks % NVS;
+                            wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
+                            uint8_t* dst = sm.data + VA_VRING + slot * V_SLOT_BYTES + part2 * 2 * BOX_BYTES + tok * 128;
+                            uint4 v[16];
+#pragma unroll
+                            for (int k = 0; k < 16; ++k) v[k] = ok ? __ldg(src + (nh * 4 + part2 * 2) * 8 + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                            for (int k = 0; k < 16; ++k)
+                                *reinterpret_cast<uint4*>(dst + (k >> 3) * BOX_BYTES + (((k & 7) ^ sw) << 4)) = v[k];
+                            fence_proxy_async_smem();
+                            mbar_arrive(smem_addr(&sm.kv_full[slot]));
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        if (MODE != MODE_DENSE) asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
         const int wq = warp & 3;                                  // TMEM lane quarter of this warp
         const int half = (warp - 4) >> 2;                         // score CTA: page of the tile this warpgroup owns
         const int r = wq * 32 + lane;                             // row inside the block = TMEM lane
@@ -621,16 +613,13 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                     mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
                     if (MODE == MODE_PREFILL) {
-                        // validity bits of the gathered tokens: token 4l+k of the tile is bit l of word k
-                        const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + SC_MASK) + (g & 3) * 4;
-                        const uint32_t m0 = km[0] >> (half * 16), m1 = km[1] >> (half * 16);
-                        const uint32_t m2 = km[2] >> (half * 16), m3 = km[3] >> (half * 16);
-                        if (((m0 & m1 & m2 & m3) & 0xffffu) != 0xffffu) {
+                        // validity bits of the gathered tokens: token 32w + l of the tile is bit l of word w
+                        const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + SC_MASK) + (g & 3) * 4 + half * 2;
+                        const uint32_t m0 = km[0], m1 = km[1];
+                        if ((m0 & m1) != 0xffffffffu) {
 #pragma unroll
-                            for (int c = 0; c < 64; ++c) {
-                                const uint32_t word = (c & 3) == 0 ? m0 : ((c & 3) == 1 ? m1 : ((c & 3) == 2 ? m2 : m3));
-                                if (!((word >> (c >> 2)) & 1u)) s[c] = 0xff800000u;      // -inf
-                            }
+                            for (int c = 0; c < 64; ++c)
+                                if (!(((c < 32 ? m0 : m1) >> (c & 31)) & 1u)) s[c] = 0xff800000u;      // -inf
                         }
                     } else {
                         const int nvalid = limit - (w.blk_begin + 2 * i + half) * PAGE;   // columns [0, nvalid) are visible
@@ -956,6 +945,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     p.out = (__nv_bfloat16*)a.out; p.lse = a.lse; p.max_logits = a.max_logits;
     p.attn_sink = a.attn_sink;
     p.indices = a.indices; p.idx_ss = a.indices_stride_s; p.topk = a.topk; p.topk_len = a.topk_length; p.s_kv = a.s_kv;
+    p.kv = (const __nv_bfloat16*)a.kv; p.kv_ss = a.kv_stride_s;
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
 
@@ -971,7 +961,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     if (pairs < 1) pairs = 1;
     if (pairs > a.s_q) pairs = a.s_q;
     dim3 grid(2, p.row_blocks, pairs);
-    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
