@@ -473,9 +473,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     } else if (MODE != MODE_DENSE && warp >= 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
         // ---------------- gather warpgroup (sparse modes): fills the K ring (score CTA) / V ring (value CTA) by index ----
-        // One thread per token: it reads its token's row from global memory (whole 32-byte sectors, many loads in
-        // flight) and writes it into the 128-byte-swizzled operand layout; invalid tokens get zeros.  The writes are
-        // generic-proxy stores, so each thread fences them for the tensor core's (async-proxy) reads before arriving.
+        // One thread per token: it copies its token's row with 16-byte cp.async (whole 32-byte sectors, no registers
+        // held, as many copies in flight as the ring has room for) into the 128-byte-swizzled operand layout; invalid
+        // tokens get zeros (zero-size source).  The ring barrier counts one arrival per thread, made by the copy
+        // engine when that thread's copies have landed.
         const int tid = threadIdx.x - 384;
         uint32_t ks = 0, g = 0;
         uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
@@ -488,25 +489,20 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                     const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
                     const bool ok = id >= 0 && id < p.s_kv;
                     const uint32_t bal = __ballot_sync(0xffffffffu, ok);
-                    if (lane == 0) kmask[(g & 3) * 4 + (warp - 12)] = bal;       // token w*32 + l of the tile is bit l of word w
+                    if (lane == 0) { kmask[(g & 3) * 4 + (warp - 12)] = bal; __threadfence_block(); }   // token w*32 + l of the tile is bit l of word w
                     const uint4* src = reinterpret_cast<const uint4*>(p.kv + (int64_t)(ok ? id : 0) * p.kv_ss);
                     uint8_t* rowdst = sm.data + SC_KRING + tid * 128;
                     const int sw = tid & 7;
                     for (int grp = 0; grp < 3; ++grp, ++ks) {
                         wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
+                        const uint32_t nbytes = ok ? 16u : 0u;                   // 0: the copy writes zeros
+                        const uint32_t rowaddr = smem_addr(rowdst);
 #pragma unroll
-                        for (int hb = 0; hb < 2; ++hb) {                          // 2 batches of 12 x 16 bytes
-                            uint4 v[12];
-#pragma unroll
-                            for (int k = 0; k < 12; ++k) v[k] = ok ? __ldg(src + grp * 24 + hb * 12 + k) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                            for (int k = 0; k < 12; ++k) {
-                                const int c16 = grp * 24 + hb * 12 + k, j = c16 >> 3, c = c16 & 7;
-                                *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = v[k];
-                            }
+                        for (int k = 0; k < 24; ++k) {
+                            const int c16 = grp * 24 + k, j = c16 >> 3, c = c16 & 7;
+                            cp_async16_zfill(rowaddr + j * K_CHUNK_BYTES + ((c ^ sw) << 4), src + c16, nbytes);
                         }
-                        fence_proxy_async_smem();
-                        mbar_arrive(smem_addr(&sm.kv_full[grp]));
+                        cp_async_arrive_noinc(smem_addr(&sm.kv_full[grp]));
                     }
                 } else {
                     const int tok = tid & 63, part2 = tid >> 6;                   // part2: boxes {0,1} or {2,3} of a slot
@@ -520,14 +516,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                             const uint32_t slot = ks % NVS;
                             wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
                             uint8_t* dst = sm.data + VA_VRING + slot * V_SLOT_BYTES + part2 * 2 * BOX_BYTES + tok * 128;
-                            uint4 v[16];
-#pragma unroll
-                            for (int k = 0; k < 16; ++k) v[k] = ok ? __ldg(src + (nh * 4 + part2 * 2) * 8 + k) : make_uint4(0, 0, 0, 0);
+                            const uint32_t nbytes = ok ? 16u : 0u;
+                            const uint32_t daddr = smem_addr(dst);
 #pragma unroll
                             for (int k = 0; k < 16; ++k)
-                                *reinterpret_cast<uint4*>(dst + (k >> 3) * BOX_BYTES + (((k & 7) ^ sw) << 4)) = v[k];
-                            fence_proxy_async_smem();
-                            mbar_arrive(smem_addr(&sm.kv_full[slot]));
+                                cp_async16_zfill(daddr + (k >> 3) * BOX_BYTES + (((k & 7) ^ sw) << 4), src + (nh * 4 + part2 * 2) * 8 + k, nbytes);
+                            cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot]));
                         }
                     }
                 }

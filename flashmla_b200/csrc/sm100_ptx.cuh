@@ -124,6 +124,15 @@ __device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* 
         ::"r"(dst), "l"(m), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
 
+// Per-thread asynchronous 16-byte copy global -> shared; src_bytes = 0 writes zeros without reading.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// Arrive on `bar` (counted among its expected arrivals) once all cp.async copies this thread issued so far have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
 // L2 eviction-priority policies for loads that should stay in (or get out of) L2.
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t pol;
