@@ -473,11 +473,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     } else if (MODE != MODE_DENSE && warp >= 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
         // ---------------- gather warpgroup (sparse modes): fills the K ring (score CTA) / V ring (value CTA) by index ----
-        // One thread per token: it copies its token's row with 16-byte cp.async (whole 32-byte sectors, no registers
-        // held, as many copies in flight as the ring has room for) into the 128-byte-swizzled operand layout; invalid
-        // tokens get zeros (zero-size source).  The ring barrier counts one arrival per thread, made by the copy
-        // engine when that thread's copies have landed.
-        const int tid = threadIdx.x - 384;
+        // Every warp owns a block of tokens; one cp.async instruction of the warp copies consecutive 16-byte pieces of
+        // ONE token row (coalesced 128-byte lines, no registers held, as many copies in flight as the ring has room
+        // for) into the 128-byte-swizzled operand layout; invalid tokens get zeros (zero-size source).  The ring
+        // barrier counts one arrival per thread, made by the copy engine when that thread's copies have landed.
+        const int gw = warp - 12;                                 // warp inside the gather warpgroup
         uint32_t ks = 0, g = 0;
         uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -485,42 +485,45 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
             const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
             for (int i = 0; i < w.ntiles; ++i, ++g) {
                 if (cta_rank == 0) {
-                    const int pos = i * 128 + tid;
+                    // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
+                    const int pos = i * 128 + gw * 32 + lane;
                     const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
                     const bool ok = id >= 0 && id < p.s_kv;
                     const uint32_t bal = __ballot_sync(0xffffffffu, ok);
-                    if (lane == 0) { kmask[(g & 3) * 4 + (warp - 12)] = bal; __threadfence_block(); }   // token w*32 + l of the tile is bit l of word w
-                    const uint4* src = reinterpret_cast<const uint4*>(p.kv + (int64_t)(ok ? id : 0) * p.kv_ss);
-                    uint8_t* rowdst = sm.data + SC_KRING + tid * 128;
-                    const int sw = tid & 7;
+                    if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }   // token 32w + l of the tile is bit l of word w
+                    const int row_id = ok ? id : -1;
                     for (int grp = 0; grp < 3; ++grp, ++ks) {
                         wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                        const uint32_t nbytes = ok ? 16u : 0u;                   // 0: the copy writes zeros
-                        const uint32_t rowaddr = smem_addr(rowdst);
-#pragma unroll
-                        for (int k = 0; k < 24; ++k) {
-                            const int c16 = grp * 24 + k, j = c16 >> 3, c = c16 & 7;
-                            cp_async16_zfill(rowaddr + j * K_CHUNK_BYTES + ((c ^ sw) << 4), src + c16, nbytes);
+                        // one instruction per row: lanes 0..23 copy the group's 24 consecutive 16-byte pieces of that row
+                        const int c16 = grp * 24 + lane, j = c16 >> 3, c = c16 & 7;
+                        const uint32_t dst0 = smem_addr(sm.data + SC_KRING) + j * K_CHUNK_BYTES + gw * 32 * 128;
+#pragma unroll 8
+                        for (int rr = 0; rr < 32; ++rr) {
+                            const int rid = __shfl_sync(0xffffffffu, row_id, rr);
+                            if (lane < 24) {
+                                const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + c16 * 8;
+                                cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
+                            }
                         }
                         cp_async_arrive_noinc(smem_addr(&sm.kv_full[grp]));
                     }
                 } else {
-                    const int tok = tid & 63, part2 = tid >> 6;                   // part2: boxes {0,1} or {2,3} of a slot
-                    const int sw = tok & 7;
+                    // warp gw owns tokens 16*gw .. 16*gw+15 of each page; one instruction copies 512 bytes of one row
                     for (int h = 0; h < 2; ++h) {
-                        const int pos = i * 128 + h * 64 + tok;
+                        const int pos = i * 128 + h * 64 + gw * 16 + (lane & 15);
                         const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
-                        const bool ok = id >= 0 && id < p.s_kv;
-                        const uint4* src = reinterpret_cast<const uint4*>(p.kv + (int64_t)(ok ? id : 0) * p.kv_ss);
+                        const int row_id = (id >= 0 && id < p.s_kv) ? id : -1;
                         for (int nh = 0; nh < 2; ++nh, ++ks) {
                             const uint32_t slot = ks % NVS;
                             wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
-                            uint8_t* dst = sm.data + VA_VRING + slot * V_SLOT_BYTES + part2 * 2 * BOX_BYTES + tok * 128;
-                            const uint32_t nbytes = ok ? 16u : 0u;
-                            const uint32_t daddr = smem_addr(dst);
-#pragma unroll
-                            for (int k = 0; k < 16; ++k)
-                                cp_async16_zfill(daddr + (k >> 3) * BOX_BYTES + (((k & 7) ^ sw) << 4), src + (nh * 4 + part2 * 2) * 8 + k, nbytes);
+                            const int box = lane >> 3, c = lane & 7;
+                            const uint32_t dst0 = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES) + box * BOX_BYTES + gw * 16 * 128;
+#pragma unroll 8
+                            for (int rr = 0; rr < 16; ++rr) {
+                                const int rid = __shfl_sync(0xffffffffu, row_id, rr);
+                                const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + (nh * 32 + lane) * 8;
+                                cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
+                            }
                             cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot]));
                         }
                     }
