@@ -141,7 +141,13 @@ int mla_sparse_decode_fwd(const mla_sparse_decode_args_t* a) {
     } else {
         MLA_CHECK_ARG(!a->extra_indices && !a->extra_topk_length, "mla_sparse_decode_fwd: extra_indices / extra_topk_length need extra_kv");
     }
-    if (a->impl == 2) return set_error(MLA_ERR_UNSUPPORTED, "mla_sparse_decode_fwd: no tcgen05 kernel for this shape");
+    if (a->impl == 2) {
+        if (!sparse_decode_sm100_supports(*a))
+            return set_error(MLA_ERR_UNSUPPORTED, "mla_sparse_decode_fwd: the tcgen05 kernel does not support this shape");
+        return launch_sparse_decode_sm100(*a);
+    }
+    // the tcgen05 kernel works on blocks of 128 rows: with 64 heads or fewer the portable kernel wastes less
+    if (a->impl == 0 && a->h_q > 64 && sparse_decode_sm100_supports(*a)) return launch_sparse_decode_sm100(*a);
     return launch_sparse_decode_portable(*a);
 }
 

@@ -35,6 +35,7 @@
 // epilogue, empty rows) of deepseek-ai/FlashMLA; the reference has no sm_100 dense decode kernel.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include <string.h>
 
 namespace mla {
 namespace sm100 {
@@ -103,10 +104,13 @@ struct Params {
     // token-sparse prefill: one "request" is one query token, its keys are gathered by index
     const int* indices; int64_t idx_ss; int topk; const int* topk_len; int s_kv;
     const __nv_bfloat16* kv; int64_t kv_ss;
+    // sparse FP8 decode: two index scopes (main cache, optional extra cache) of 656-byte token records
+    const uint8_t* kvb[2]; int64_t kvb_sblock[2]; int pbs[2]; int nblocks[2];
+    const int* sidx[2]; int64_t sidx_sb[2], sidx_ss[2]; int stopk[2]; const int* stopk_len[2];
     const float* attn_sink; float* max_logits;
 };
 
-enum { MODE_DENSE = 0, MODE_PREFILL = 1 };
+enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
 #ifndef MLA_GATHER_LANES
 #define MLA_GATHER_LANES 8
 #endif
@@ -118,6 +122,7 @@ static_assert(SC_LSUM + ROWS * 4 <= DATA_BYTES, "score CTA scratch must fit");
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
     int req, blk_begin, blk_end, ntiles, seqlen, is_split, slot;
+    int len0, len1, nblk0;      // sparse decode: valid positions of the two index scopes, blocks of the first scope
 };
 
 template <int MODE>
@@ -137,6 +142,36 @@ struct Walker<MODE_DENSE> {
         w.seqlen = p.seqlens[req];
         w.blk_begin = req == m.begin_req_idx ? m.begin_block_idx : 0;
         w.blk_end = req == m.end_req_idx ? m.end_block_idx : (w.seqlen + PAGE - 1) / PAGE;
+        if (w.blk_end < w.blk_begin) w.blk_end = w.blk_begin;
+        w.ntiles = (w.blk_end - w.blk_begin + 1) / 2;
+        w.is_split = req == m.begin_req_idx ? m.is_first_req_splitted : (req == m.end_req_idx ? m.is_last_req_splitted : 0);
+        w.slot = p.num_splits[req] + (req == m.begin_req_idx ? m.begin_split_idx : 0);
+        return w;
+    }
+    __device__ void next() { ++req; }
+};
+
+// sparse FP8 decode: like dense decode, but a request's "sequence" is its top-k list: blocks [0, nblk0) index the
+// main cache, the following blocks the optional extra cache (block counts as in the tile scheduler)
+template <>
+struct Walker<MODE_SPARSE_DECODE> {
+    mla_sched_meta_t m;
+    const Params& p;
+    int req;
+    __device__ Walker(const Params& p_, int part) : p(p_) { m = p_.meta[part]; req = m.begin_req_idx; }
+    __device__ bool valid() const { return m.begin_req_idx < p.b && req <= m.end_req_idx; }
+    __device__ Work get() const {
+        Work w;
+        w.req = req;
+        const int l0 = p.stopk_len[0] ? p.stopk_len[0][req] : p.stopk[0];
+        const int l1 = p.stopk[1] ? (p.stopk_len[1] ? p.stopk_len[1][req] : p.stopk[1]) : 0;
+        w.len0 = min(max(l0, 0), p.stopk[0]);
+        w.len1 = min(max(l1, 0), p.stopk[1]);
+        w.nblk0 = max((l0 + PAGE - 1) / PAGE, 1);
+        const int total = w.nblk0 + (l1 + PAGE - 1) / PAGE;
+        w.seqlen = total * PAGE;
+        w.blk_begin = req == m.begin_req_idx ? m.begin_block_idx : 0;
+        w.blk_end = req == m.end_req_idx ? m.end_block_idx : total;
         if (w.blk_end < w.blk_begin) w.blk_end = w.blk_begin;
         w.ntiles = (w.blk_end - w.blk_begin + 1) / 2;
         w.is_split = req == m.begin_req_idx ? m.is_first_req_splitted : (req == m.end_req_idx ? m.is_last_req_splitted : 0);
@@ -213,6 +248,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return r;
 }
 
+// 16 e4m3 values (one uint4) times an fp32 scale -> 16 bf16 (two uint4), one rounding: bf16(fp32(e4m3) * scale).
+__device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
+        __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
+        const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
+        const float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+        o[2 * i] = pack_bf16(f0.x * scale, f0.y * scale);
+        o[2 * i + 1] = pack_bf16(f1.x * scale, f1.y * scale);
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+__device__ __forceinline__ const uint8_t* shfl_ptr(const uint8_t* ptr, int src_lane) {
+    const unsigned long long v = reinterpret_cast<unsigned long long>(ptr);
+    const uint32_t lo = __shfl_sync(0xffffffffu, (uint32_t)v, src_lane);
+    const uint32_t hi = __shfl_sync(0xffffffffu, (uint32_t)(v >> 32), src_lane);
+    return reinterpret_cast<const uint8_t*>(((unsigned long long)hi << 32) | lo);
+}
+
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
 attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
@@ -221,8 +279,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();          // 0 = score CTA, 1 = value CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row_blk = blockIdx.y % p.row_blocks;
-    const int hk = blockIdx.y / p.row_blocks;
+    const int row_blk = MODE == MODE_SPARSE_DECODE ? 0 : blockIdx.y % p.row_blocks;
+    const int hk = MODE == MODE_SPARSE_DECODE ? 0 : blockIdx.y / p.row_blocks;
     const int part = blockIdx.z;
 
     if ((smem_addr(smem_raw) & 1023u) != 0) {              // the swizzled tiles need a 1024-byte aligned base
@@ -480,6 +538,101 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
         const int gw = warp - 12;                                 // warp inside the gather warpgroup
         uint32_t ks = 0, g = 0;
         uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
+        if (MODE == MODE_SPARSE_DECODE) {
+            // FP8 records: index -> (page, offset) -> 656-byte record; the 512 e4m3 values are de-quantised with their
+            // group's fp32 scale (one rounding to bf16) on the way into the swizzled operand layout, the 64 bf16 RoPE
+            // values are copied.  A "piece" is 16 values (16 bytes of e4m3, 32 bytes of bf16); lanes are spread over the
+            // pieces of two token rows per step so that a ring group (3 chunks of 64 dims) is filled by one pass.
+            const int tq = blockIdx.y;
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+                const Work w = wk.get();
+                const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
+                const int* idx1 = p.stopk[1] ? p.sidx[1] + (int64_t)w.req * p.sidx_sb[1] + (int64_t)tq * p.sidx_ss[1] : nullptr;
+                auto lookup = [&](int blk, int off) -> const uint8_t* {
+                    if (blk >= w.blk_end) return nullptr;
+                    const int scope = blk >= w.nblk0 ? 1 : 0;
+                    const int pos = (scope ? blk - w.nblk0 : blk) * PAGE + off;
+                    if (pos >= (scope ? w.len1 : w.len0)) return nullptr;
+                    const int id = __ldg((scope ? idx1 : idx0) + pos);
+                    const int pbs = p.pbs[scope];
+                    if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return nullptr;
+                    return p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * 656;
+                };
+                for (int i = 0; i < w.ntiles; ++i, ++g) {
+                    const int blk0 = w.blk_begin + 2 * i;
+                    if (cta_rank == 0) {
+                        // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
+                        const int tok = gw * 32 + lane;
+                        const uint8_t* rec = lookup(blk0 + (tok >> 6), tok & 63);
+                        const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
+                        if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
+                        uint8_t* kbase = sm.data + SC_KRING + gw * 32 * 128;
+                        for (int grp = 0; grp < 3; ++grp, ++ks) {
+                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
+                            // groups 0, 1: 12 pieces per row (lanes 0-11 first row, 12-23 second row of the pair);
+                            // group 2: 8 pieces + 8 RoPE pieces per row (lanes 0-15 first row, 16-31 second row)
+                            const int per_row = grp < 2 ? 12 : 16;
+                            const int sub = lane / per_row, q = lane - sub * per_row;
+                            const bool active = sub < 2;
+                            const bool is_rope = grp == 2 && q >= 8;
+                            const int piece = grp < 2 ? grp * 12 + q : 24 + (q & 7);      // e4m3 piece, or RoPE piece q - 8
+#pragma unroll 4
+                            for (int rp = 0; rp < 16; ++rp) {
+                                const int rr = 2 * rp + (active ? sub : 0);
+                                const uint8_t* r = shfl_ptr(rec, rr);
+                                if (!active) continue;
+                                uint8_t* rowdst = kbase + rr * 128;
+                                const int sw = rr & 7;
+                                if (is_rope) {
+                                    const uint4 v = r ? __ldg(reinterpret_cast<const uint4*>(r + 528) + (q - 8)) : make_uint4(0, 0, 0, 0);
+                                    *reinterpret_cast<uint4*>(rowdst + 8 * K_CHUNK_BYTES + (((q - 8) ^ sw) << 4)) = v;
+                                } else {
+                                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                                    if (r) {
+                                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(r) + piece);
+                                        const float scale = __ldg(reinterpret_cast<const float*>(r + 512) + (piece >> 3));
+                                        dequant16(raw, scale, lo, hi);
+                                    }
+                                    const int j = piece >> 2, c = (piece & 3) * 2;
+                                    *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = lo;
+                                    *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + (((c + 1) ^ sw) << 4)) = hi;
+                                }
+                            }
+                            fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's reads
+                            mbar_arrive(smem_addr(&sm.kv_full[grp]));
+                        }
+                    } else {
+                        // value CTA: warp gw owns tokens 16*gw .. 16*gw+15 of each page; a slot is 256 dims = 16 pieces per row
+                        for (int h = 0; h < 2; ++h) {
+                            const uint8_t* rec = lookup(blk0 + h, gw * 16 + (lane & 15));
+                            for (int nh = 0; nh < 2; ++nh, ++ks) {
+                                const uint32_t slot = ks % NVS;
+                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
+                                const int sub = lane >> 4, q = lane & 15, piece = nh * 16 + q;
+                                uint8_t* vbase = sm.data + VA_VRING + slot * V_SLOT_BYTES + (q >> 2) * BOX_BYTES + gw * 16 * 128;
+                                const int c = (q & 3) * 2;
+#pragma unroll 4
+                                for (int rp = 0; rp < 8; ++rp) {
+                                    const int rr = 2 * rp + sub;
+                                    const uint8_t* r = shfl_ptr(rec, rr);
+                                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                                    if (r) {
+                                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(r) + piece);
+                                        const float scale = __ldg(reinterpret_cast<const float*>(r + 512) + (piece >> 3));
+                                        dequant16(raw, scale, lo, hi);
+                                    }
+                                    const int sw = rr & 7;
+                                    *reinterpret_cast<uint4*>(vbase + rr * 128 + ((c ^ sw) << 4)) = lo;
+                                    *reinterpret_cast<uint4*>(vbase + rr * 128 + (((c + 1) ^ sw) << 4)) = hi;
+                                }
+                                fence_proxy_async_smem();
+                                mbar_arrive(smem_addr(&sm.kv_full[slot]));
+                            }
+                        }
+                    }
+                }
+            }
+        } else
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
             const Work w = wk.get();
             const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
@@ -538,8 +691,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
         const uint32_t tlane = tmem + ((uint32_t)(wq * 32) << 16);
         const int row = row_blk * ROWS + r;                       // row inside the (request, kv head) group
         const bool row_ok = row < p.rows;
-        const int t = row_ok ? row / p.g : 0;
-        const int hd = hk * p.g + (row_ok ? row - t * p.g : 0);
+        // dense: rows are (query token, head of the kv group); sparse decode: the CTA pair serves one query token
+        const int t = MODE == MODE_SPARSE_DECODE ? (int)blockIdx.y : (row_ok ? row / p.g : 0);
+        const int hd = MODE == MODE_SPARSE_DECODE ? (row_ok ? row : 0) : hk * p.g + (row_ok ? row - t * p.g : 0);
         uint32_t g = 0, nreq = 0;
 
         if (cta_rank == 0) {
@@ -609,7 +763,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                     tc_fence_before();
                     mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
-                    if (MODE == MODE_PREFILL) {
+                    if (MODE != MODE_DENSE) {
                         // validity bits of the gathered tokens: token 32w + l of the tile is bit l of word w
                         const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + SC_MASK) + (g & 3) * 4 + half * 2;
                         const uint32_t m0 = km[0], m1 = km[1];
@@ -760,7 +914,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                 const float L = sm.fin_l[r], M = sm.fin_m[r];
                 const bool empty = !(L > 0.f) || !has_tiles;          // also catches NaN
                 float scale = empty ? 0.f : 1.f / L;
-                if (MODE == MODE_PREFILL && p.attn_sink && !empty && row_ok)
+                if (MODE != MODE_DENSE && !w.is_split && p.attn_sink && !empty && row_ok)
                     scale = 1.f / (L + exp2f(p.attn_sink[hd] * kLog2e - M));
                 if (!w.is_split) {
                     __nv_bfloat16* orow = MODE == MODE_PREFILL
@@ -959,6 +1113,49 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     if (pairs > a.s_q) pairs = a.s_q;
     dim3 grid(2, p.row_blocks, pairs);
     attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    MLA_CHECK_CUDA(cudaGetLastError());
+    return MLA_OK;
+}
+
+bool sparse_decode_sm100_supports(const mla_sparse_decode_args_t& a) {
+    if (a.d_qk != 576 || a.d_v != 512) return false;
+    if (a.h_q > 128 || a.s_q > 65535 || a.num_sm_parts > 65535) return false;
+    if (!(a.sm_scale > 0.f)) return false;
+    return true;
+}
+
+int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
+    using namespace sm100;
+    Params p = {};
+    p.b = a.b; p.s_q = a.s_q; p.h_q = a.h_q; p.h_kv = 1; p.g = a.h_q; p.rows = a.h_q;
+    p.causal = 0;
+    p.scale_log2 = a.sm_scale * kLog2e;
+    p.q = (const __nv_bfloat16*)a.q; p.q_sb = a.q_stride_b; p.q_ss = a.q_stride_s; p.q_sh = a.q_stride_h;
+    p.out = (__nv_bfloat16*)a.out; p.o_sb = a.o_stride_b; p.o_ss = a.o_stride_s; p.o_sh = a.o_stride_h;
+    p.lse = a.lse; p.l_sb = a.lse_stride_b; p.l_ss = a.lse_stride_s; p.l_sh = a.lse_stride_h;
+    p.attn_sink = a.attn_sink;
+    p.meta = a.meta; p.num_splits = a.num_splits; p.lse_accum = a.lse_accum; p.o_accum = a.o_accum;
+    p.status = a.status;
+    p.row_blocks = 1;
+    p.kvb[0] = (const uint8_t*)a.kv; p.kvb_sblock[0] = a.kv_stride_block_bytes; p.pbs[0] = a.page_block_size; p.nblocks[0] = a.num_blocks;
+    p.sidx[0] = a.indices; p.sidx_sb[0] = a.indices_stride_b; p.sidx_ss[0] = a.indices_stride_s; p.stopk[0] = a.topk;
+    p.stopk_len[0] = a.topk_length;
+    p.kvb[1] = (const uint8_t*)a.extra_kv; p.kvb_sblock[1] = a.extra_kv_stride_block_bytes;
+    p.pbs[1] = a.extra_page_block_size > 0 ? a.extra_page_block_size : 1; p.nblocks[1] = a.extra_num_blocks;
+    p.sidx[1] = a.extra_indices; p.sidx_sb[1] = a.extra_indices_stride_b; p.sidx_ss[1] = a.extra_indices_stride_s;
+    p.stopk[1] = a.extra_kv ? a.extra_topk : 0; p.stopk_len[1] = a.extra_topk_length;
+
+    int dev = 0;
+    MLA_CHECK_CUDA(cudaGetDevice(&dev));
+    static bool configured[64] = {};
+    if (dev >= 64 || !configured[dev]) {
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_SPARSE_DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        if (dev < 64) configured[dev] = true;
+    }
+    CUtensorMap unused_map;
+    memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers with its own threads, no TMA descriptor
+    dim3 grid(2, a.s_q, a.num_sm_parts);
+    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

@@ -26,6 +26,18 @@ def _decode(q, kv, indices, sm_scale, attn_sink=None, topk_length=None, extra_kv
     return out, lse
 
 
+@pytest.mark.parametrize("impl", [1, 2])
+def test_sparse_decode_golden_both_kernel_families(golden_dir, impl):
+    """The portable kernel (1) and the tcgen05 kernel (2, rows padded to 128) on the reference-generated vectors,
+    which cover attn_sink, topk_length, the extra cache and a request without any valid index."""
+    import flashmla_b200 as fm
+    fm.set_impl(impl)
+    try:
+        test_sparse_decode_golden(golden_dir)
+    finally:
+        fm.set_impl(0)
+
+
 def test_sparse_decode_golden(golden_dir):
     for c in torch.load(os.path.join(golden_dir, "sparse_decode.pt"), weights_only=False):
         kv = c["kv_bytes"].view(torch.float8_e4m3fn)
@@ -116,6 +128,16 @@ def test_sparse_prefill_golden(golden_dir):
         assert_out_close("out", out, c["out"])
         assert_lse_close("max_logits", mx, c["max_logits"])
         assert_lse_close("lse", lse, c["lse"])
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_sparse_prefill_golden_both_kernel_families(golden_dir, impl):
+    import flashmla_b200 as fm
+    fm.set_impl(impl)
+    try:
+        test_sparse_prefill_golden(golden_dir)
+    finally:
+        fm.set_impl(0)
 
 
 @pytest.mark.parametrize("s_q,h_q,s_kv,topk", [(62, 128, 2000, 256), (7, 64, 300, 128), (33, 128, 128, 384)])
