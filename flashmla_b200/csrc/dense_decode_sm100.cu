@@ -249,6 +249,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // 16 e4m3 values (one uint4) times an fp32 scale -> 16 bf16 (two uint4), one rounding: bf16(fp32(e4m3) * scale).
+// (A conversion-free variant that places the e4m3 magnitude bits into an fp32 word and multiplies by scale * 2^120 is
+// bit-identical but needs more instructions per value and measured slower.)
 __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t o[8];
@@ -576,26 +578,40 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                             const bool active = sub < 2;
                             const bool is_rope = grp == 2 && q >= 8;
                             const int piece = grp < 2 ? grp * 12 + q : 24 + (q & 7);      // e4m3 piece, or RoPE piece q - 8
-#pragma unroll 4
-                            for (int rp = 0; rp < 16; ++rp) {
-                                const int rr = 2 * rp + (active ? sub : 0);
-                                const uint8_t* r = shfl_ptr(rec, rr);
-                                if (!active) continue;
-                                uint8_t* rowdst = kbase + rr * 128;
-                                const int sw = rr & 7;
-                                if (is_rope) {
-                                    const uint4 v = r ? __ldg(reinterpret_cast<const uint4*>(r + 528) + (q - 8)) : make_uint4(0, 0, 0, 0);
-                                    *reinterpret_cast<uint4*>(rowdst + 8 * K_CHUNK_BYTES + (((q - 8) ^ sw) << 4)) = v;
-                                } else {
-                                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                                    if (r) {
-                                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(r) + piece);
-                                        const float scale = __ldg(reinterpret_cast<const float*>(r + 512) + (piece >> 3));
-                                        dequant16(raw, scale, lo, hi);
+                            // loads of 8 row pairs are issued before any of them is used (memory-level parallelism);
+                            // rows without a record read a dummy address and are zeroed afterwards
+                            const int srcoff = is_rope ? 528 + (q - 8) * 16 : piece * 16;
+#pragma unroll
+                            for (int rp0 = 0; rp0 < 16; rp0 += 8) {
+                                uint4 raw[8];
+                                float sc[8];
+                                bool have[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const int rr = 2 * (rp0 + u) + (active ? sub : 0);
+                                    const uint8_t* r = shfl_ptr(rec, rr);
+                                    have[u] = r != nullptr;
+                                    const uint8_t* rs = have[u] ? r : p.kvb[0];
+                                    raw[u] = __ldg(reinterpret_cast<const uint4*>(rs + srcoff));
+                                    sc[u] = is_rope ? 1.f : __ldg(reinterpret_cast<const float*>(rs + 512) + (piece >> 3));
+                                }
+                                if (active) {
+#pragma unroll
+                                    for (int u = 0; u < 8; ++u) {
+                                        const int rr = 2 * (rp0 + u) + sub;
+                                        uint8_t* rowdst = kbase + rr * 128;
+                                        const int sw = rr & 7;
+                                        if (is_rope) {
+                                            *reinterpret_cast<uint4*>(rowdst + 8 * K_CHUNK_BYTES + (((q - 8) ^ sw) << 4)) =
+                                                have[u] ? raw[u] : make_uint4(0, 0, 0, 0);
+                                        } else {
+                                            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+                                            if (have[u]) dequant16(raw[u], sc[u], lo, hi);
+                                            const int j = piece >> 2, c = (piece & 3) * 2;
+                                            *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = lo;
+                                            *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + (((c + 1) ^ sw) << 4)) = hi;
+                                        }
                                     }
-                                    const int j = piece >> 2, c = (piece & 3) * 2;
-                                    *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = lo;
-                                    *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + (((c + 1) ^ sw) << 4)) = hi;
                                 }
                             }
                             fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's reads
@@ -611,16 +627,22 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                 const int sub = lane >> 4, q = lane & 15, piece = nh * 16 + q;
                                 uint8_t* vbase = sm.data + VA_VRING + slot * V_SLOT_BYTES + (q >> 2) * BOX_BYTES + gw * 16 * 128;
                                 const int c = (q & 3) * 2;
-#pragma unroll 4
-                                for (int rp = 0; rp < 8; ++rp) {
-                                    const int rr = 2 * rp + sub;
-                                    const uint8_t* r = shfl_ptr(rec, rr);
+                                uint4 raw[8];
+                                float sc[8];
+                                bool have[8];
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const uint8_t* r = shfl_ptr(rec, 2 * u + sub);
+                                    have[u] = r != nullptr;
+                                    const uint8_t* rs = have[u] ? r : p.kvb[0];
+                                    raw[u] = __ldg(reinterpret_cast<const uint4*>(rs) + piece);
+                                    sc[u] = __ldg(reinterpret_cast<const float*>(rs + 512) + (piece >> 3));
+                                }
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const int rr = 2 * u + sub;
                                     uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                                    if (r) {
-                                        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(r) + piece);
-                                        const float scale = __ldg(reinterpret_cast<const float*>(r + 512) + (piece >> 3));
-                                        dequant16(raw, scale, lo, hi);
-                                    }
+                                    if (have[u]) dequant16(raw[u], sc[u], lo, hi);
                                     const int sw = rr & 7;
                                     *reinterpret_cast<uint4*>(vbase + rr * 128 + ((c ^ sw) << 4)) = lo;
                                     *reinterpret_cast<uint4*>(vbase + rr * 128 + (((c + 1) ^ sw) << 4)) = hi;

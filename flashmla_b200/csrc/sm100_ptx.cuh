@@ -133,6 +133,11 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Fire-and-forget prefetch of `bytes` (multiple of 16, 16-byte aligned address) from global memory into L2.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // L2 eviction-priority policies for loads that should stay in (or get out of) L2.
 __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     uint64_t pol;
