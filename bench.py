@@ -32,7 +32,7 @@ D_QK, D_V = 576, 512
 # workloads: inputs + algorithmic bytes / flops (conventions of the reference's own test scripts:
 # tests/test_flash_mla_dense_decoding.py:174-190, tests/lib.py:345-402)
 # ------------------------------------------------------------------------------------------------------
-def make_workload(name, device, seed):
+def make_workload(name, device, seed, prefill_sq=4096):
     from flashmla_b200 import workloads as W
     if name in ("dense", "dense_sq2"):
         s_q = 2 if name == "dense_sq2" else 1
@@ -66,7 +66,7 @@ def make_workload(name, device, seed):
                     flops=2.0 * h_q * valid * (D_QK + D_V),
                     desc=f"sparse fp8 MLA decode b={b} h_q={h_q} s_kv={s_kv} topk={topk} (5% padded -1) 656B records scale=amax/448")
     if name == "sparse_prefill":
-        s_q, h_q, s_kv, topk = 4096, 128, 32768, 2048
+        s_q, h_q, s_kv, topk = prefill_sq, 128, 32768, 2048
         d = W.sparse_prefill_inputs(s_q, h_q, s_kv, topk, causal_base=28672, seed=seed, device=device, data_on_device=True)
         valid = s_q * topk
         return dict(kind="sparse_prefill", inputs=d, s_q=s_q, b=1, h_q=h_q, tokens=valid,
@@ -294,6 +294,7 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill"])
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prefill-sq", type=int, default=4096, help="query tokens of the sparse_prefill workload (smaller for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -305,7 +306,7 @@ def main():
         if rank != 0:
             return
         dev = "cuda:0" if torch.cuda.is_available() else "cpu"
-        w = make_workload(args.workload, dev, seed=0)
+        w = make_workload(args.workload, dev, seed=0, prefill_sq=args.prefill_sq)
         metric, unit, units_per_step = metric_of(w)
         # each "step" is one bounded sample of the workload on all host cores
         vals = []
@@ -335,7 +336,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     fm.set_impl(args.kernel)
 
-    w = make_workload(args.workload, dev, seed=rank)
+    w = make_workload(args.workload, dev, seed=rank, prefill_sq=args.prefill_sq)
     w["meta"] = fm.get_mla_metadata()[0]
     metric, unit, units_per_step = metric_of(w)
 
