@@ -92,6 +92,7 @@ static_assert(sizeof(Smem) <= 232448, "shared memory budget");
 
 struct Params {
     int b, s_q, h_q, h_kv, g, rows, causal, num_blocks;
+    int head_chunks;                       // dense mode: 64-column chunks between two kv heads of a cache row
     float scale_log2;
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
     __nv_bfloat16* out; int64_t o_sb, o_ss, o_sh;
@@ -111,10 +112,6 @@ struct Params {
 };
 
 enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
-#ifndef MLA_GATHER_LANES
-#define MLA_GATHER_LANES 8
-#endif
-constexpr int GATHER_LANES = MLA_GATHER_LANES;     // lanes of the producer warp that issue row gathers
 constexpr int SC_MASK = SC_END;          // score CTA, prefill: validity bits of the last 4 tiles, [4][4] words
 constexpr int SC_LSUM = SC_MASK + 64;    // score CTA: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
 static_assert(SC_LSUM + ROWS * 4 <= DATA_BYTES, "score CTA scratch must fit");
@@ -230,11 +227,22 @@ __device__ __forceinline__ void trace_ev(int part, int row_blk, int ev, uint32_t
         g_trace[ev][g] = t;
     }
 }
+// Coarse per-partition timeline: [partition][event][occurrence]
+__device__ unsigned long long g_span[128][8][8];
+__device__ __forceinline__ void span_ev(int part, int row_blk, int ev, int n) {
+    if (part < 128 && row_blk == 0 && n < 8) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_span[part][ev][n] = t;
+    }
+}
+#define SPAN(ev, n) span_ev(part, row_blk, ev, n)
 #define TRACE(ev, g) trace_ev(part, row_blk, ev, g)
 #define TRACE_CLOCK(ev, g) do { if (part == 0 && row_blk == 0 && (g) < 512) g_trace[ev][g] = (unsigned long long)clock64(); } while (0)
 #else
 #define TRACE(ev, g)
 #define TRACE_CLOCK(ev, g)
+#define SPAN(ev, n)
 #endif
 
 __device__ __forceinline__ float ex2(float x) {
@@ -275,7 +283,7 @@ __device__ __forceinline__ const uint8_t* shfl_ptr(const uint8_t* ptr, int src_l
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
-attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
+attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
     using WalkerT = Walker<MODE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -313,13 +321,14 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
         for (int i = 0; i < NPB; ++i)
             mbar_arrive_expect_tx(smem_addr(&sm.p_full[i]), P_SUB_BYTES + ((i & 1) == 0 ? 4 * SIDE_BYTES : 0));
         fence_mbar_init();
-        if (MODE == MODE_DENSE) prefetch_tensormap(&kmap);
+        if (MODE == MODE_DENSE) prefetch_tensormap(cta_rank == 0 ? &kmap : &vmap);
     }
     if (warp == 1) { tmem_alloc(smem_addr(&sm.tmem_base), 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
+    if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
     const uint32_t tmem = sm.tmem_base;
     Waiter wt(p.status, &sm.aborted);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
@@ -334,7 +343,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
         if (MODE != MODE_DENSE) {
             // sparse modes: the gather warpgroup fills the rings
         } else if (lane == 0) {
-            uint32_t ks = 0;                               // ring slot counter (K chunks or V half-pages)
+            uint32_t ks = 0;                               // ring slot counter (K groups or V half-pages)
+            const int chunk0 = hk * p.head_chunks;         // the kv head's first 64-column chunk in the tensor maps
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
@@ -359,11 +369,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                             const uint32_t bar = smem_addr(&sm.kv_full[grp]);
                             mbar_arrive_expect_tx(bar, K_GROUP_BYTES);
                             const uint32_t dst = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES);
-#pragma unroll
-                            for (int c = 0; c < 3; ++c) {
-                                tma_load_4d(dst + c * K_CHUNK_BYTES, &kmap, bar, (grp * 3 + c) * 64, hk, 0, page0);
-                                tma_load_4d(dst + c * K_CHUNK_BYTES + BOX_BYTES, &kmap, bar, (grp * 3 + c) * 64, hk, 0, page1);
-                            }
+                            // one box per page: 3 chunks x 64 tokens land as [8-token group][chunk][8 x 128 B]
+                            tma_load_5d(dst, &kmap, bar, 0, 0, chunk0 + grp * 3, 0, page0);
+                            tma_load_5d(dst + K_GROUP_BYTES / 2, &kmap, bar, 0, 0, chunk0 + grp * 3, 0, page1);
                         }
                     } else {
                         for (int h = 0; h < 2; ++h) {
@@ -374,8 +382,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                 const uint32_t bar = smem_addr(&sm.kv_full[slot]);
                                 mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
                                 const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) tma_load_4d(dst + j * BOX_BYTES, &kmap, bar, (nh * 4 + j) * 64, hk, 0, page);
+                                // one box: 4 chunks x 64 tokens as [8-token group][chunk][8 x 128 B]
+                                tma_load_5d(dst, &vmap, bar, 0, 0, chunk0 + nh * 4, 0, page);
                             }
                         }
                     }
@@ -396,6 +404,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     wt.wait<false>(&sm.q_ready, nreq & 1, 2);
+                    SPAN(1, nreq);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         const uint32_t sb = g & 1;
                         wt.wait<false>(&sm.s_empty[sb], ((g >> 1) & 1) ^ 1, 4);
@@ -407,6 +416,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                         // 32-bit adds only and the loop is fully unrolled: one thread issues everything, so its
                         // instruction latency is the issue rate.
                         constexpr uint32_t hi = sw128_desc_hi(1024);
+                        // K operand: the gather modes store a tile as 9 chunks of [128 tokens][128 B]; the dense mode's
+                        // TMA boxes interleave the 3 chunks of a ring group inside every 8-token group.
+                        constexpr uint32_t hi_k = sw128_desc_hi(MODE == MODE_DENSE ? 3 * 1024 : 1024);
                         // The probe of the next group's barrier is issued before this group's MMAs so that its
                         // latency hides behind them (the MMA queue is shallow: time the issuing thread spends
                         // waiting is time the tensor pipe idles).
@@ -421,12 +433,13 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
 #pragma unroll
                             for (int c = 0; c < 3; ++c) {
                                 const int j = grp * 3 + c;
-                                const uint32_t b_lo = kring_lo + j * (K_CHUNK_BYTES >> 4);
+                                const uint32_t b_lo = MODE == MODE_DENSE ? kring_lo + grp * (K_GROUP_BYTES >> 4) + c * (1024 >> 4)
+                                                                         : kring_lo + j * (K_CHUNK_BYTES >> 4);
 #pragma unroll
                                 for (int k4 = 0; k4 < 4; ++k4) {
                                     const uint32_t acc = (j > 0 || k4 > 0) ? 1u : 0u;
-                                    if (j < Q_TMEM_CHUNKS) mma_ts_lohi(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, b_lo + k4 * 2, hi, idesc, acc);
-                                    else mma_ss_lohi(d_tmem, q78_lo + (j - Q_TMEM_CHUNKS) * (16384 >> 4) + k4 * 2, hi, b_lo + k4 * 2, hi, idesc, acc);
+                                    if (j < Q_TMEM_CHUNKS) mma_ts_lohi(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, b_lo + k4 * 2, hi_k, idesc, acc);
+                                    else mma_ss_lohi(d_tmem, q78_lo + (j - Q_TMEM_CHUNKS) * (16384 >> 4) + k4 * 2, hi, b_lo + k4 * 2, hi_k, idesc, acc);
                                 }
                             }
                             tc_commit(kv_empty0 + grp * 8);
@@ -434,12 +447,16 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                         tc_commit(smem_addr(&sm.s_full[sb]));
                         TRACE(2, g);
                     }
+                    SPAN(2, nreq);
                 }
             } else {
                 constexpr uint32_t idesc = make_idesc_bf16(ROWS, 256, true);
-                constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(1024);
+                // V operand (MN-major): LBO = stride between 64-dim chunks, SBO = stride between 8-token groups.  Gather
+                // modes: 4 chunks of [64 tokens][128 B]; dense mode: chunks interleaved inside every 8-token group.
+                constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(MODE == MODE_DENSE ? 4 * 1024 : 1024);
+                constexpr uint32_t v_kstep = (MODE == MODE_DENSE ? 2 * 4096 : 2 * 1024) >> 4;      // 16 tokens
                 const uint32_t p_lo = sw128_desc_lo(smem_addr(sm.data + VA_P), 16);
-                const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), BOX_BYTES);
+                const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), MODE == MODE_DENSE ? 1024 : BOX_BYTES);
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
@@ -457,7 +474,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                 const uint32_t b_lo = vring_lo + slot * (V_SLOT_BYTES >> 4);
 #pragma unroll
                                 for (int kt = 0; kt < PAGE / 16; ++kt)
-                                    mma_ss_lohi(tmem + nh * 256, a_lo + kt * 2, hi_a, b_lo + kt * (2048 >> 4), hi_b, idesc,
+                                    mma_ss_lohi(tmem + nh * 256, a_lo + kt * 2, hi_a, b_lo + kt * v_kstep, hi_b, idesc,
                                                 (i > 0 || h > 0 || kt > 0) ? 1u : 0u);
                                 tc_commit(smem_addr(&sm.kv_empty[slot]));
                             }
@@ -919,7 +936,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                                 const int nz = (PAGE - first) * 4 * 8;              // rows x boxes x 16-byte chunks
                                 for (int k = threadIdx.x - 128; k < nz; k += 128) {
                                     const int chunk = k & 7, box = (k >> 3) & 3, rr = first + (k >> 5);
-                                    *reinterpret_cast<uint4*>(vst + box * BOX_BYTES + rr * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+                                    // dense V slot: [8-token group][chunk][8 rows x 128 B]
+                                    *reinterpret_cast<uint4*>(vst + (rr >> 3) * 4096 + box * 1024 + (rr & 7) * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
                                 }
                             }
                             fence_proxy_async_smem();
@@ -931,7 +949,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                 // ---- epilogue -----------------------------------------------------------------------------------
                 const bool has_tiles = w.ntiles > 0;
                 if (has_tiles) wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 110);
+                if (threadIdx.x == 128) SPAN(3, nreq);
                 wt.wait<true>(&sm.fin_full, nreq & 1, 111);
+                if (threadIdx.x == 128) SPAN(4, nreq);
                 tc_fence_after();
                 const float L = sm.fin_l[r], M = sm.fin_m[r];
                 const bool empty = !(L > 0.f) || !has_tiles;          // also catches NaN
@@ -989,6 +1009,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
                     if (row_ok) p.lse_accum[arow] = empty ? -INFINITY : log2f(L) + M;
                 }
                 tc_fence_before();
+                if (threadIdx.x == 128) SPAN(5, nreq);
                 mbar_arrive_remote(remote_fin_empty);        // fin_l / fin_m may be rewritten
             }
         }
@@ -997,6 +1018,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const Params p) {
     // ---- wind down: both CTAs leave together, tensor memory is released -----------------------------------
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) SPAN(6 + cta_rank, 0);
     if (sm.aborted) {
         // a bounded wait ran out somewhere: give copies that may still be in flight time to land
         const long long t0 = clock64();
@@ -1028,6 +1050,9 @@ static EncodeTiledFn get_encode_fn() {
 extern "C" int mla_debug_trace_copy(void* host_dst) {
     return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_trace, sizeof(sm100::g_trace));
 }
+extern "C" int mla_debug_span_copy(void* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_span, sizeof(sm100::g_span));
+}
 #endif
 
 bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
@@ -1038,6 +1063,8 @@ bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
     if (a.k_stride_block <= 0 || a.k_stride_row <= 0 || a.k_stride_head <= 0) return false;
     if (a.k_stride_block >= lim || a.k_stride_row >= lim || a.k_stride_head >= lim) return false;
     if (a.k_stride_block % 8 || a.k_stride_row % 8 || a.k_stride_head % 8) return false;
+    // the kv heads of a row are addressed as 64-column chunks of one tensor-map dimension
+    if (a.h_kv > 1 && a.k_stride_head % 64) return false;
     const int rows = a.s_q * (a.h_q / a.h_kv);
     const int64_t row_blocks = (rows + 127) / 128;
     if (row_blocks * a.h_kv > 65535 || a.num_sm_parts > 65535) return false;
@@ -1050,14 +1077,25 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
 
-    CUtensorMap kmap;
-    cuuint64_t dims[4] = {(cuuint64_t)D_QK, (cuuint64_t)a.h_kv, (cuuint64_t)a.page_block_size, (cuuint64_t)a.num_blocks};
-    cuuint64_t strides[3] = {(cuuint64_t)a.k_stride_head * 2, (cuuint64_t)a.k_stride_row * 2, (cuuint64_t)a.k_stride_block * 2};
-    cuuint32_t box[4] = {64, 1, 64, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(a.k_cache), dims, strides, box, estr,
+    // The cache as a 5-D tensor (64 columns of a chunk, 8 tokens, chunks, 8 token groups, pages): one box brings
+    // all 64 tokens of a page for 3 (K) or 4 (V) chunks in a single instruction, and lands as
+    // [token group][chunk][8 rows x 128 B] - 1 KiB swizzle atoms that the MMA descriptors walk with a stride of
+    // 3 or 4 KiB between token groups.  (The per-instruction cost of TMA is what limits one SM's fill rate: 8 KiB
+    // boxes stream at 35-45 GB/s per SM, 24 KiB boxes at about 90.)
+    const int head_chunks = a.h_kv > 1 ? (int)(a.k_stride_head / 64) : 9;
+    CUtensorMap kmap, vmap;
+    cuuint64_t dims[5] = {64, 8, (cuuint64_t)((a.h_kv - 1) * head_chunks + 9), 8, (cuuint64_t)a.num_blocks};
+    cuuint64_t strides[4] = {(cuuint64_t)a.k_stride_row * 2, 128, (cuuint64_t)a.k_stride_row * 16, (cuuint64_t)a.k_stride_block * 2};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    cuuint32_t kbox[5] = {64, 8, 3, 8, 1};
+    cuuint32_t vbox[5] = {64, 8, 4, 8, 1};
+    CUresult r = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(a.k_cache), dims, strides, kbox, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS)
+        r = encode(&vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(a.k_cache), dims, strides, vbox, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
 
     Params p = {};
@@ -1073,6 +1111,7 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
     p.num_blocks = a.num_blocks;
+    p.head_chunks = head_chunks;
 
     static bool configured[64] = {};
     int dev = 0;
@@ -1082,7 +1121,7 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
         if (dev < 64) configured[dev] = true;
     }
     dim3 grid(2, p.row_blocks * a.h_kv, a.num_sm_parts);
-    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, vmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1097,18 +1136,8 @@ bool sparse_prefill_sm100_supports(const mla_sparse_prefill_args_t& a) {
 
 int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     using namespace sm100;
-    EncodeTiledFn encode = get_encode_fn();
-    if (!encode) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    // kv as a 2-D tensor (576, s_kv); rows are fetched four at a time by index (gather4), 64 columns per box
     CUtensorMap kmap;
-    cuuint64_t dims[2] = {(cuuint64_t)D_QK, (cuuint64_t)a.s_kv};
-    cuuint64_t strides[1] = {(cuuint64_t)a.kv_stride_s * 2};
-    cuuint32_t box[2] = {64, 1};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(a.kv), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    memset(&kmap, 0, sizeof(kmap));     // rows are gathered with cp.async by the kernel's own threads, no TMA descriptor
 
     Params p = {};
     p.b = a.s_q; p.s_q = 1; p.h_q = a.h_q; p.h_kv = 1; p.g = a.h_q; p.rows = a.h_q;
@@ -1134,7 +1163,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     if (pairs < 1) pairs = 1;
     if (pairs > a.s_q) pairs = a.s_q;
     dim3 grid(2, p.row_blocks, pairs);
-    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, p);
+    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1177,7 +1206,7 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     CUtensorMap unused_map;
     memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers with its own threads, no TMA descriptor
     dim3 grid(2, a.s_q, a.num_sm_parts);
-    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, p);
+    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

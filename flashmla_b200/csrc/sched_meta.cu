@@ -10,7 +10,7 @@
 // overhead is taken from the next request and the partition ends.
 //
 // Layout: one CTA; the per-request lengths are staged in shared memory by all threads, then one
-// thread runs the O(b + num_sm_parts) serial walk (a few microseconds; the result is cached by the
+// thread runs the O(b + num_sm_parts) serial walk over precomputed block counts (no division in the loop; the result is cached by the
 // caller for the whole decode step).
 #include "common.cuh"
 
@@ -19,7 +19,7 @@ namespace mla {
 __global__ void __launch_bounds__(128, 1)
 sched_meta_kernel(const mla_sched_meta_args_t a) {
     extern __shared__ int smem_i[];
-    int* seq_s = smem_i;                 // [b]  effective length of every request
+    int* nblk_s = smem_i;                // [b]  KV blocks of every request; -1 marks a zero-length request (1 block)
     int* nsplit_s = smem_i + a.b;        // [b + 1]
     __shared__ int total_s;
     const int b = a.b, bs = a.block_size_n, F = a.fixed_overhead_num_blocks;
@@ -39,8 +39,9 @@ sched_meta_kernel(const mla_sched_meta_args_t a) {
                 s += a.extra_topk_length ? a.extra_topk_length[i] : a.extra_topk;
             }
         }
-        seq_s[i] = s;
-        local_total += max(s - 1, 0) / bs + 1 + F;     // a zero-length request still costs one block
+        const int nblk = max(s - 1, 0) / bs + 1;       // a zero-length request still costs one block
+        nblk_s[i] = s == 0 ? -1 : nblk;
+        local_total += nblk + F;
     }
     atomicAdd(&total_s, local_total);
     __syncthreads();
@@ -50,7 +51,7 @@ sched_meta_kernel(const mla_sched_meta_args_t a) {
         const int payload = (total_s + P - 1) / P + F;
         int now_req = 0, now_block = 0, now_split = 0, cum = 0;
         nsplit_s[0] = 0;
-        const int last_block_req0 = max(seq_s[0] - 1, 0) / bs;
+        const int last_block_req0 = abs(nblk_s[0]) - 1;
         for (int p = 0; p < P; ++p) {
             mla_sched_meta_t m;
             m.begin_req_idx = now_req;
@@ -62,8 +63,7 @@ sched_meta_kernel(const mla_sched_meta_args_t a) {
             m.is_first_req_splitted = now_block != 0;
             int remain = payload;
             while (now_req < b) {
-                const int nblk = max(seq_s[now_req] - 1, 0) / bs + 1;
-                const int rest = nblk - now_block;
+                const int rest = abs(nblk_s[now_req]) - now_block;
                 if (remain >= rest + F) {
                     cum += now_split + 1;
                     nsplit_s[now_req + 1] = cum;
@@ -85,11 +85,10 @@ sched_meta_kernel(const mla_sched_meta_args_t a) {
                 m.end_block_idx = now_block;
             } else {
                 m.end_req_idx = now_req - 1;
-                const int s_prev = seq_s[now_req - 1];
-                m.end_block_idx = s_prev == 0 ? 0 : max(s_prev - 1, 0) / bs + 1;
+                m.end_block_idx = max(nblk_s[now_req - 1], 0);
             }
-            const int s_end = seq_s[m.end_req_idx];
-            m.is_last_req_splitted = (m.end_block_idx != max(s_end - 1, 0) / bs + 1) && s_end != 0;
+            const int n_end = nblk_s[m.end_req_idx];
+            m.is_last_req_splitted = n_end > 0 && m.end_block_idx != n_end;
             if (m.begin_req_idx == m.end_req_idx) {
                 m.is_first_req_splitted = m.is_last_req_splitted = (m.is_first_req_splitted || m.is_last_req_splitted);
             }
