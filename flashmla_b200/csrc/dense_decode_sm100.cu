@@ -203,13 +203,16 @@ struct Walker<MODE_PREFILL> {
 // Bounded wait helper: after the first expiry the thread stops waiting altogether.
 struct Waiter {
     bool aborted = false;
+    bool parked;                         // park the thread between probes instead of spinning
     int* status;
     uint32_t* smem_flag;
-    __device__ Waiter(int* st, uint32_t* flag) : status(st), smem_flag(flag) {}
+    __device__ Waiter(int* st, uint32_t* flag, bool park = false) : parked(park), status(st), smem_flag(flag) {}
     template <bool CLUSTER>
     __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
         if (aborted) return;
-        if (!mbar_wait_bounded<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT)) {
+        const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT)
+                               : mbar_wait_bounded<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT);
+        if (!ok) {
             aborted = true;
             *smem_flag = 1;
             if (status) { atomicCAS(status, 0, code); atomicAdd(status + 1, 1); }
@@ -236,6 +239,8 @@ __device__ __forceinline__ void span_ev(int part, int row_blk, int ev, int n) {
         g_span[part][ev][n] = t;
     }
 }
+__device__ long long g_gtrace[4][512];
+#define GTRACE(ev, n) do { if (part == 0 && row_blk == 0 && gw == 0 && lane == 0 && cta_rank == 0 && (n) < 512) g_gtrace[ev][n] = clock64(); } while (0)
 #define SPAN(ev, n) span_ev(part, row_blk, ev, n)
 #define TRACE(ev, g) trace_ev(part, row_blk, ev, g)
 #define TRACE_CLOCK(ev, g) do { if (part == 0 && row_blk == 0 && (g) < 512) g_trace[ev][g] = (unsigned long long)clock64(); } while (0)
@@ -243,6 +248,7 @@ __device__ __forceinline__ void span_ev(int part, int row_blk, int ev, int n) {
 #define TRACE(ev, g)
 #define TRACE_CLOCK(ev, g)
 #define SPAN(ev, n)
+#define GTRACE(ev, n)
 #endif
 
 __device__ __forceinline__ float ex2(float x) {
@@ -330,7 +336,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
     if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
     const uint32_t tmem = sm.tmem_base;
-    Waiter wt(p.status, &sm.aborted);
+    // FP8 decode: the gather warps need the issue slots that waiting warps would otherwise spin on
+    Waiter wt(p.status, &sm.aborted, MODE == MODE_SPARSE_DECODE && warp < 12);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
 
     // =====================================================================================================
@@ -558,11 +565,72 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         uint32_t ks = 0, g = 0;
         uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
         if (MODE == MODE_SPARSE_DECODE) {
-            // FP8 records: index -> (page, offset) -> 656-byte record; the 512 e4m3 values are de-quantised with their
-            // group's fp32 scale (one rounding to bf16) on the way into the swizzled operand layout, the 64 bf16 RoPE
-            // values are copied.  A "piece" is 16 values (16 bytes of e4m3, 32 bytes of bf16); lanes are spread over the
-            // pieces of two token rows per step so that a ring group (3 chunks of 64 dims) is filled by one pass.
+            // FP8 records: index -> (page, offset) -> 656-byte record = 512 e4m3 | 4 fp32 scales | 64 bf16 RoPE.
+            // A "piece" is 16 e4m3 values (16 bytes) that de-quantise (one rounding: bf16(fp32(e4m3) * scale)) into two
+            // 16-byte slots of a 128-byte operand row.  Two decoupled steps per ring element (a K group of 3 chunks in
+            // the score CTA, a V slot of 4 chunks in the value CTA):
+            //   copy:    cp.async brings every raw piece straight into the UPPER of its own two destination slots (one
+            //            instruction per token row, lanes = pieces: coalesced, no registers held), RoPE pieces into
+            //            their final place;
+            //   convert: two elements later, when the copies have landed, every lane expands the pieces of its own
+            //            row in place (it reads a slot only it will overwrite; 16-byte accesses, conflict-free thanks
+            //            to the swizzle) and the element is handed to the tensor core.
+            // The element's copies are in flight while the two elements before it are converted: that is what covers
+            // the latency of the scattered record reads.  Record pointers and scales of the next tile are fetched
+            // while the current one is processed.
             const int tq = blockIdx.y;
+            uint32_t n_el = 0;                               // elements issued so far (all requests of this CTA)
+            float4 sc_cur = make_float4(0.f, 0.f, 0.f, 0.f), sc_prev = sc_cur;
+            const uint32_t kring = smem_addr(sm.data + SC_KRING);
+            const uint32_t vring = smem_addr(sm.data + VA_VRING);
+            // converts K group `grp` (chunks 3grp..3grp+2; group 2 = chunks 6, 7 + RoPE chunk) for row `lane` of this warp
+            auto convert_k = [&](int grp, const float4& sc) {
+                const int rr = gw * 32 + lane, sw = rr & 7;
+                const int nconv = grp < 2 ? 3 : 2;
+#pragma unroll
+                for (int cj = 0; cj < 3; ++cj) {
+                    if (cj < nconv) {
+                        const int j = grp * 3 + cj;
+                        uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + rr * 128;
+                        const float scale = (j >> 1) == 0 ? sc.x : (j >> 1) == 1 ? sc.y : (j >> 1) == 2 ? sc.z : sc.w;
+                        uint4 raw[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            uint4 lo, hi;
+                            dequant16(raw[k], scale, lo, hi);
+                            *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
+                            *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
+                        }
+                    }
+                }
+            };
+            // converts half of the 16 pieces of row (lane & 15) of this warp's 16 rows of V slot `slot` (dims nh*256..)
+            auto convert_v = [&](uint32_t slot, int nh, const float4& sc) {
+                const int rr = gw * 16 + (lane & 15), sw = rr & 7, hb = lane >> 4;
+                const float s0 = nh ? sc.z : sc.x, s1 = nh ? sc.w : sc.y;
+                const float scale = hb ? s1 : s0;
+#pragma unroll
+                for (int cj = 0; cj < 2; ++cj) {
+                    uint8_t* rowp = sm.data + VA_VRING + slot * V_SLOT_BYTES + (hb * 2 + cj) * BOX_BYTES + rr * 128;
+                    uint4 raw[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        uint4 lo, hi;
+                        dequant16(raw[k], scale, lo, hi);
+                        *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
+                        *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
+                    }
+                }
+            };
+            // hands element e (already converted by this thread) to the MMA warp
+            auto publish = [&](uint64_t* bar) {
+                fence_proxy_async_smem();              // generic-proxy stores -> visible to the tensor core's reads
+                mbar_arrive(smem_addr(bar));
+            };
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
@@ -577,99 +645,111 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return nullptr;
                     return p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * 656;
                 };
-                for (int i = 0; i < w.ntiles; ++i, ++g) {
-                    const int blk0 = w.blk_begin + 2 * i;
-                    if (cta_rank == 0) {
-                        // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
-                        const int tok = gw * 32 + lane;
-                        const uint8_t* rec = lookup(blk0 + (tok >> 6), tok & 63);
+                auto scales_of = [&](const uint8_t* rec) {
+                    return rec ? __ldg(reinterpret_cast<const float4*>(rec + 512)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                };
+                if (cta_rank == 0) {
+                    // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
+                    const int tok = gw * 32 + lane;
+                    const uint8_t* rec_next = w.ntiles > 0 ? lookup(w.blk_begin + (tok >> 6), tok & 63) : nullptr;
+                    float4 sc_next = scales_of(rec_next);
+                    for (int i = 0; i < w.ntiles; ++i, ++g) {
+                        const uint8_t* rec = rec_next;
+                        sc_prev = sc_cur;
+                        sc_cur = sc_next;
+                        if (i + 1 < w.ntiles) {
+                            rec_next = lookup(w.blk_begin + 2 * (i + 1) + (tok >> 6), tok & 63);
+                            sc_next = scales_of(rec_next);
+                        }
                         const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
                         if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
-                        uint8_t* kbase = sm.data + SC_KRING + gw * 32 * 128;
-                        for (int grp = 0; grp < 3; ++grp, ++ks) {
+#pragma unroll
+                        for (int grp = 0; grp < 3; ++grp, ++ks, ++n_el) {
+                            GTRACE(0, n_el);
                             wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                            // groups 0, 1: 12 pieces per row (lanes 0-11 first row, 12-23 second row of the pair);
-                            // group 2: 8 pieces + 8 RoPE pieces per row (lanes 0-15 first row, 16-31 second row)
-                            const int per_row = grp < 2 ? 12 : 16;
-                            const int sub = lane / per_row, q = lane - sub * per_row;
-                            const bool active = sub < 2;
-                            const bool is_rope = grp == 2 && q >= 8;
-                            const int piece = grp < 2 ? grp * 12 + q : 24 + (q & 7);      // e4m3 piece, or RoPE piece q - 8
-                            // loads of 8 row pairs are issued before any of them is used (memory-level parallelism);
-                            // rows without a record read a dummy address and are zeroed afterwards
-                            const int srcoff = is_rope ? 528 + (q - 8) * 16 : piece * 16;
-#pragma unroll
-                            for (int rp0 = 0; rp0 < 16; rp0 += 8) {
-                                uint4 raw[8];
-                                float sc[8];
-                                bool have[8];
-#pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const int rr = 2 * (rp0 + u) + (active ? sub : 0);
-                                    const uint8_t* r = shfl_ptr(rec, rr);
-                                    have[u] = r != nullptr;
-                                    const uint8_t* rs = have[u] ? r : p.kvb[0];
-                                    raw[u] = __ldg(reinterpret_cast<const uint4*>(rs + srcoff));
-                                    sc[u] = is_rope ? 1.f : __ldg(reinterpret_cast<const float*>(rs + 512) + (piece >> 3));
-                                }
-                                if (active) {
-#pragma unroll
-                                    for (int u = 0; u < 8; ++u) {
-                                        const int rr = 2 * (rp0 + u) + sub;
-                                        uint8_t* rowdst = kbase + rr * 128;
-                                        const int sw = rr & 7;
-                                        if (is_rope) {
-                                            *reinterpret_cast<uint4*>(rowdst + 8 * K_CHUNK_BYTES + (((q - 8) ^ sw) << 4)) =
-                                                have[u] ? raw[u] : make_uint4(0, 0, 0, 0);
-                                        } else {
-                                            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                                            if (have[u]) dequant16(raw[u], sc[u], lo, hi);
-                                            const int j = piece >> 2, c = (piece & 3) * 2;
-                                            *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + ((c ^ sw) << 4)) = lo;
-                                            *reinterpret_cast<uint4*>(rowdst + j * K_CHUNK_BYTES + (((c + 1) ^ sw) << 4)) = hi;
-                                        }
-                                    }
-                                }
+                            GTRACE(1, n_el);
+                            // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row
+                            const int nl = grp < 2 ? 12 : 16;
+                            const bool is_rope = grp == 2 && lane >= 8;
+                            const int q = grp * 12 + lane;                    // raw piece index in the row (lanes < 12 / 8)
+                            const int srcoff = is_rope ? 528 + (lane - 8) * 16 : q * 16;
+                            const int dslot = is_rope ? lane - 8 : 2 * (q & 3) + 1;
+                            const uint32_t dst0 = kring + (is_rope ? 8 : (q >> 2)) * K_CHUNK_BYTES + gw * 32 * 128;
+#pragma unroll 8
+                            for (int rr = 0; rr < 32; ++rr) {
+                                const uint8_t* r = shfl_ptr(rec, rr);
+                                if (lane < nl)
+                                    cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + srcoff, r ? 16u : 0u);
                             }
-                            fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's reads
-                            mbar_arrive(smem_addr(&sm.kv_full[grp]));
+                            cp_async_commit();
+                            GTRACE(2, n_el);
+                            // convert the element issued two steps ago
+                            if (n_el >= 2) {
+                                cp_async_wait_group<2>();
+                                __syncwarp();
+                                GTRACE(3, n_el);
+                                const int pg = (grp + 1) % 3;                 // its group; it belongs to the previous tile unless grp == 2
+                                convert_k(pg, grp == 2 ? sc_cur : sc_prev);
+                                publish(&sm.kv_full[pg]);
+                            }
                         }
-                    } else {
-                        // value CTA: warp gw owns tokens 16*gw .. 16*gw+15 of each page; a slot is 256 dims = 16 pieces per row
+                    }
+                } else {
+                    // value CTA: warp gw owns tokens 16*gw .. 16*gw+15 of each page; lanes l and l + 16 look up the same token
+                    const int tok = gw * 16 + (lane & 15);
+                    const uint8_t* rec_next = w.ntiles > 0 ? lookup(w.blk_begin, tok) : nullptr;
+                    float4 sc_next = scales_of(rec_next);
+                    for (int i = 0; i < w.ntiles; ++i, ++g) {
+#pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const uint8_t* rec = lookup(blk0 + h, gw * 16 + (lane & 15));
-                            for (int nh = 0; nh < 2; ++nh, ++ks) {
+                            const uint8_t* rec = rec_next;
+                            sc_prev = sc_cur;
+                            sc_cur = sc_next;
+                            const int nblk = w.blk_begin + 2 * i + h + 1;
+                            if (h == 0 || i + 1 < w.ntiles) {
+                                rec_next = lookup(nblk, tok);
+                                sc_next = scales_of(rec_next);
+                            }
+#pragma unroll
+                            for (int nh = 0; nh < 2; ++nh, ++ks, ++n_el) {
                                 const uint32_t slot = ks % NVS;
                                 wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
-                                const int sub = lane >> 4, q = lane & 15, piece = nh * 16 + q;
-                                uint8_t* vbase = sm.data + VA_VRING + slot * V_SLOT_BYTES + (q >> 2) * BOX_BYTES + gw * 16 * 128;
-                                const int c = (q & 3) * 2;
-                                uint4 raw[8];
-                                float sc[8];
-                                bool have[8];
-#pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const uint8_t* r = shfl_ptr(rec, 2 * u + sub);
-                                    have[u] = r != nullptr;
-                                    const uint8_t* rs = have[u] ? r : p.kvb[0];
-                                    raw[u] = __ldg(reinterpret_cast<const uint4*>(rs) + piece);
-                                    sc[u] = __ldg(reinterpret_cast<const float*>(rs + 512) + (piece >> 3));
+                                // copy: 16 raw pieces per row (dims nh*256 .. nh*256+255), lanes 0..15
+                                const int q = nh * 16 + (lane & 15);
+                                const uint32_t dst0 = vring + slot * V_SLOT_BYTES + ((lane & 15) >> 2) * BOX_BYTES + gw * 16 * 128;
+                                const int dslot = 2 * (lane & 3) + 1;
+#pragma unroll 8
+                                for (int rr = 0; rr < 16; ++rr) {
+                                    const uint8_t* r = shfl_ptr(rec, rr);
+                                    if (lane < 16)
+                                        cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
                                 }
-#pragma unroll
-                                for (int u = 0; u < 8; ++u) {
-                                    const int rr = 2 * u + sub;
-                                    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-                                    if (have[u]) dequant16(raw[u], sc[u], lo, hi);
-                                    const int sw = rr & 7;
-                                    *reinterpret_cast<uint4*>(vbase + rr * 128 + ((c ^ sw) << 4)) = lo;
-                                    *reinterpret_cast<uint4*>(vbase + rr * 128 + (((c + 1) ^ sw) << 4)) = hi;
+                                cp_async_commit();
+                                if (n_el >= 2) {
+                                    cp_async_wait_group<2>();
+                                    __syncwarp();
+                                    // the element two steps back: same page if nh == 1 ... (h, nh) -> (h - 1, nh) in slot order
+                                    const uint32_t pslot = (ks - 2) % NVS;
+                                    convert_v(pslot, nh, sc_prev);
+                                    publish(&sm.kv_full[pslot]);
                                 }
-                                fence_proxy_async_smem();
-                                mbar_arrive(smem_addr(&sm.kv_full[slot]));
                             }
                         }
                     }
                 }
+            }
+            // drain: the last two elements
+            if (n_el >= 2) {
+                cp_async_wait_group<1>();
+                __syncwarp();
+                if (cta_rank == 0) { convert_k(1, sc_cur); publish(&sm.kv_full[1]); }
+                else { const uint32_t pslot = (ks - 2) % NVS; convert_v(pslot, 0, sc_cur); publish(&sm.kv_full[pslot]); }
+            }
+            if (n_el >= 1) {
+                cp_async_wait_group<0>();
+                __syncwarp();
+                if (cta_rank == 0) { convert_k(2, sc_cur); publish(&sm.kv_full[2]); }
+                else { const uint32_t pslot = (ks - 1) % NVS; convert_v(pslot, 1, sc_cur); publish(&sm.kv_full[pslot]); }
             }
         } else
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -1049,6 +1129,9 @@ static EncodeTiledFn get_encode_fn() {
 #ifdef MLA_TRACE
 extern "C" int mla_debug_trace_copy(void* host_dst) {
     return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_trace, sizeof(sm100::g_trace));
+}
+extern "C" int mla_debug_gtrace_copy(void* host_dst) {
+    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_gtrace, sizeof(sm100::g_gtrace));
 }
 extern "C" int mla_debug_span_copy(void* host_dst) {
     return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_span, sizeof(sm100::g_span));

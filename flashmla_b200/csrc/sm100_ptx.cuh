@@ -82,6 +82,36 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return ok != 0;
 }
 
+// try_wait with a suspend-time hint (ns): the thread is parked by the hardware until the phase completes or the time is
+// up, instead of spinning on the issue slots that the other warps of its scheduler need.
+template <bool CLUSTER_SCOPE>
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    if (CLUSTER_SCOPE)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait that parks the thread between probes.
+template <bool CLUSTER_SCOPE>
+__device__ __forceinline__ bool mbar_wait_bounded_parked(uint32_t bar, uint32_t parity, long long limit_cycles) {
+    if (CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_hint<CLUSTER_SCOPE>(bar, parity, 20000u)) return true;
+        if (clock64() - t0 > limit_cycles) return false;
+    }
+}
+
 // Bounded wait: gives up after `limit_cycles` SM clock cycles and returns false.
 template <bool CLUSTER_SCOPE>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit_cycles) {
@@ -139,6 +169,10 @@ __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
 // Arrive on `bar` (counted among its expected arrivals) once all cp.async copies this thread issued so far have landed.
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's committed cp.async groups are still in flight.
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
