@@ -635,12 +635,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 const Work w = wk.get();
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
                 const int* idx1 = p.stopk[1] ? p.sidx[1] + (int64_t)w.req * p.sidx_sb[1] + (int64_t)tq * p.sidx_ss[1] : nullptr;
-                auto lookup = [&](int blk, int off) -> const uint8_t* {
-                    if (blk >= w.blk_end) return nullptr;
+                // index -> record address in two steps, so that the index of a tile can be loaded two tiles ahead and
+                // turned into an address (and a scale load) one tile ahead without waiting on memory
+                auto load_id = [&](int blk, int off) -> int {
+                    if (blk >= w.blk_end) return -1;
                     const int scope = blk >= w.nblk0 ? 1 : 0;
                     const int pos = (scope ? blk - w.nblk0 : blk) * PAGE + off;
-                    if (pos >= (scope ? w.len1 : w.len0)) return nullptr;
-                    const int id = __ldg((scope ? idx1 : idx0) + pos);
+                    if (pos >= (scope ? w.len1 : w.len0)) return -1;
+                    return __ldg((scope ? idx1 : idx0) + pos);
+                };
+                auto rec_of = [&](int blk, int id) -> const uint8_t* {
+                    const int scope = blk >= w.nblk0 ? 1 : 0;
                     const int pbs = p.pbs[scope];
                     if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return nullptr;
                     return p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * 656;
@@ -651,16 +656,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 if (cta_rank == 0) {
                     // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
                     const int tok = gw * 32 + lane;
-                    const uint8_t* rec_next = w.ntiles > 0 ? lookup(w.blk_begin + (tok >> 6), tok & 63) : nullptr;
+                    const int myblk = w.blk_begin + (tok >> 6);              // this lane's block of tile 0
+                    const uint8_t* rec_next = rec_of(myblk, load_id(myblk, tok & 63));
                     float4 sc_next = scales_of(rec_next);
+                    int id_next = load_id(myblk + 2, tok & 63);              // tile 1
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         const uint8_t* rec = rec_next;
                         sc_prev = sc_cur;
                         sc_cur = sc_next;
-                        if (i + 1 < w.ntiles) {
-                            rec_next = lookup(w.blk_begin + 2 * (i + 1) + (tok >> 6), tok & 63);
-                            sc_next = scales_of(rec_next);
-                        }
+                        rec_next = rec_of(myblk + 2 * (i + 1), id_next);
+                        sc_next = scales_of(rec_next);
+                        id_next = load_id(myblk + 2 * (i + 2), tok & 63);
                         const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
                         if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
 #pragma unroll
@@ -697,8 +703,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 } else {
                     // value CTA: warp gw owns tokens 16*gw .. 16*gw+15 of each page; lanes l and l + 16 look up the same token
                     const int tok = gw * 16 + (lane & 15);
-                    const uint8_t* rec_next = w.ntiles > 0 ? lookup(w.blk_begin, tok) : nullptr;
+                    const uint8_t* rec_next = rec_of(w.blk_begin, load_id(w.blk_begin, tok));
                     float4 sc_next = scales_of(rec_next);
+                    int id_next = load_id(w.blk_begin + 1, tok);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
@@ -706,10 +713,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             sc_prev = sc_cur;
                             sc_cur = sc_next;
                             const int nblk = w.blk_begin + 2 * i + h + 1;
-                            if (h == 0 || i + 1 < w.ntiles) {
-                                rec_next = lookup(nblk, tok);
-                                sc_next = scales_of(rec_next);
-                            }
+                            rec_next = rec_of(nblk, id_next);
+                            sc_next = scales_of(rec_next);
+                            id_next = load_id(nblk + 1, tok);
 #pragma unroll
                             for (int nh = 0; nh < 2; ++nh, ++ks, ++n_el) {
                                 const uint32_t slot = ks % NVS;
