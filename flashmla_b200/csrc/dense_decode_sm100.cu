@@ -336,8 +336,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
     if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
     const uint32_t tmem = sm.tmem_base;
-    // FP8 decode: the gather warps need the issue slots that waiting warps would otherwise spin on
-    Waiter wt(p.status, &sm.aborted, MODE == MODE_SPARSE_DECODE && warp < 12);
+    // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
+    Waiter wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
 
     // =====================================================================================================
@@ -761,35 +761,70 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
             const Work w = wk.get();
             const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
+            // the index of a tile's token is loaded one tile ahead (a load that is used at once costs its latency)
+            int id_next = -1;
+            if (cta_rank == 0) { const int pos0 = gw * 32 + lane; id_next = pos0 < w.seqlen ? __ldg(idx + pos0) : -1; }
+            int vid_next = -1;                       // value CTA: index of this lane's token of the next page
+            if (cta_rank == 1) { const int pos0 = gw * 16 + (lane & 15); vid_next = pos0 < w.seqlen ? __ldg(idx + pos0) : -1; }
             for (int i = 0; i < w.ntiles; ++i, ++g) {
                 if (cta_rank == 0) {
                     // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
-                    const int pos = i * 128 + gw * 32 + lane;
-                    const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                    const int id = id_next;
+                    { const int posn = (i + 1) * 128 + gw * 32 + lane; id_next = posn < w.seqlen ? __ldg(idx + posn) : -1; }
                     const bool ok = id >= 0 && id < p.s_kv;
                     const uint32_t bal = __ballot_sync(0xffffffffu, ok);
                     if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }   // token 32w + l of the tile is bit l of word w
                     const int row_id = ok ? id : -1;
-                    for (int grp = 0; grp < 3; ++grp, ++ks) {
-                        wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                        // one instruction per row: lanes 0..23 copy the group's 24 consecutive 16-byte pieces of that row
-                        const int c16 = grp * 24 + lane, j = c16 >> 3, c = c16 & 7;
-                        const uint32_t dst0 = smem_addr(sm.data + SC_KRING) + j * K_CHUNK_BYTES + gw * 32 * 128;
+                    // A copy instruction costs the warp the same whatever its active lanes, so a token row (72 pieces of
+                    // 16 bytes) is copied by two full-warp instructions (chunks 0-3, chunks 4-7) and the RoPE chunk of
+                    // four rows by a third: 72 instructions per 32 rows.  The ring barriers still count per group of 3
+                    // chunks: every group's arrival is issued once all copies that touch it have been issued.
+                    const uint32_t par = ((ks / NKS) & 1) ^ 1;
+                    const uint32_t ring0 = smem_addr(sm.data + SC_KRING) + gw * 32 * 128;
+                    const int c = lane & 7;
+                    GTRACE(0, ks);
+                    wt.wait<false>(&sm.kv_empty[0], par, 201);
+                    wt.wait<false>(&sm.kv_empty[1], par, 201);
+                    GTRACE(1, ks);
+                    {
+                        const uint32_t dst0 = ring0 + (lane >> 3) * K_CHUNK_BYTES;
 #pragma unroll 8
                         for (int rr = 0; rr < 32; ++rr) {
                             const int rid = __shfl_sync(0xffffffffu, row_id, rr);
-                            if (lane < 24) {
-                                const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + c16 * 8;
-                                cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
-                            }
+                            const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + lane * 8;
+                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
                         }
-                        cp_async_arrive_noinc(smem_addr(&sm.kv_full[grp]));
                     }
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[0]));
+                    GTRACE(2, ks);
+                    wt.wait<false>(&sm.kv_empty[2], par, 201);
+                    {
+                        const uint32_t dst0 = ring0 + (4 + (lane >> 3)) * K_CHUNK_BYTES;
+#pragma unroll 8
+                        for (int rr = 0; rr < 32; ++rr) {
+                            const int rid = __shfl_sync(0xffffffffu, row_id, rr);
+                            const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + (32 + lane) * 8;
+                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
+                        }
+                    }
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[1]));
+                    {
+                        const uint32_t dst0 = ring0 + 8 * K_CHUNK_BYTES;
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) {
+                            const int rr = 4 * q4 + (lane >> 3);
+                            const int rid = __shfl_sync(0xffffffffu, row_id, rr);
+                            const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + (64 + c) * 8;
+                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
+                        }
+                    }
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[2]));
+                    ks += 3;
                 } else {
                     // warp gw owns tokens 16*gw .. 16*gw+15 of each page; one instruction copies 512 bytes of one row
                     for (int h = 0; h < 2; ++h) {
-                        const int pos = i * 128 + h * 64 + gw * 16 + (lane & 15);
-                        const int id = pos < w.seqlen ? __ldg(idx + pos) : -1;
+                        const int id = vid_next;
+                        { const int posn = i * 128 + (h + 1) * 64 + gw * 16 + (lane & 15); vid_next = posn < w.seqlen ? __ldg(idx + posn) : -1; }
                         const int row_id = (id >= 0 && id < p.s_kv) ? id : -1;
                         for (int nh = 0; nh < 2; ++nh, ++ks) {
                             const uint32_t slot = ks % NVS;
