@@ -671,33 +671,38 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
 #pragma unroll
                         for (int grp = 0; grp < 3; ++grp, ++ks, ++n_el) {
-                            GTRACE(0, n_el);
-                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                            GTRACE(1, n_el);
-                            // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row
-                            const int nl = grp < 2 ? 12 : 16;
-                            const bool is_rope = grp == 2 && lane >= 8;
-                            const int q = grp * 12 + lane;                    // raw piece index in the row (lanes < 12 / 8)
-                            const int srcoff = is_rope ? 528 + (lane - 8) * 16 : q * 16;
-                            const int dslot = is_rope ? lane - 8 : 2 * (q & 3) + 1;
-                            const uint32_t dst0 = kring + (is_rope ? 8 : (q >> 2)) * K_CHUNK_BYTES + gw * 32 * 128;
-#pragma unroll 8
-                            for (int rr = 0; rr < 32; ++rr) {
-                                const uint8_t* r = shfl_ptr(rec, rr);
-                                if (lane < nl)
-                                    cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + srcoff, r ? 16u : 0u);
-                            }
-                            cp_async_commit();
-                            GTRACE(2, n_el);
-                            // convert the element issued two steps ago
+                            // first convert the element whose copies were issued two steps ago (one newer group of copies
+                            // may still be in flight), so that the MMA warp works on it while this step's copies are issued
                             if (n_el >= 2) {
-                                cp_async_wait_group<2>();
+                                cp_async_wait_group<1>();
                                 __syncwarp();
                                 GTRACE(3, n_el);
                                 const int pg = (grp + 1) % 3;                 // its group; it belongs to the previous tile unless grp == 2
                                 convert_k(pg, grp == 2 ? sc_cur : sc_prev);
                                 publish(&sm.kv_full[pg]);
                             }
+                            GTRACE(0, n_el);
+                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
+                            GTRACE(1, n_el);
+                            // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row.  A copy
+                            // instruction costs the warp the same whatever its active lanes: each one serves two rows.
+                            const int per_row = grp < 2 ? 12 : 16;
+                            const int sub = lane / per_row, ql = lane - sub * per_row;
+                            const bool active = sub < 2;
+                            const bool is_rope = grp == 2 && ql >= 8;
+                            const int q = grp * 12 + ql;                      // raw piece index in the row
+                            const int srcoff = is_rope ? 528 + (ql - 8) * 16 : q * 16;
+                            const int dslot = is_rope ? ql - 8 : 2 * (q & 3) + 1;
+                            const uint32_t dst0 = kring + (is_rope ? 8 : (q >> 2)) * K_CHUNK_BYTES + gw * 32 * 128;
+#pragma unroll 8
+                            for (int u = 0; u < 16; ++u) {
+                                const int rr = 2 * u + (active ? sub : 0);
+                                const uint8_t* r = shfl_ptr(rec, rr);
+                                if (active)
+                                    cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + srcoff, r ? 16u : 0u);
+                            }
+                            cp_async_commit();
+                            GTRACE(2, n_el);
                         }
                     }
                 } else {
@@ -718,27 +723,28 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             id_next = load_id(nblk + 1, tok);
 #pragma unroll
                             for (int nh = 0; nh < 2; ++nh, ++ks, ++n_el) {
-                                const uint32_t slot = ks % NVS;
-                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
-                                // copy: 16 raw pieces per row (dims nh*256 .. nh*256+255), lanes 0..15
-                                const int q = nh * 16 + (lane & 15);
-                                const uint32_t dst0 = vring + slot * V_SLOT_BYTES + ((lane & 15) >> 2) * BOX_BYTES + gw * 16 * 128;
-                                const int dslot = 2 * (lane & 3) + 1;
-#pragma unroll 8
-                                for (int rr = 0; rr < 16; ++rr) {
-                                    const uint8_t* r = shfl_ptr(rec, rr);
-                                    if (lane < 16)
-                                        cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
-                                }
-                                cp_async_commit();
                                 if (n_el >= 2) {
-                                    cp_async_wait_group<2>();
+                                    cp_async_wait_group<1>();
                                     __syncwarp();
                                     // the element two steps back: same page if nh == 1 ... (h, nh) -> (h - 1, nh) in slot order
                                     const uint32_t pslot = (ks - 2) % NVS;
                                     convert_v(pslot, nh, sc_prev);
                                     publish(&sm.kv_full[pslot]);
                                 }
+                                const uint32_t slot = ks % NVS;
+                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
+                                // copy: 16 raw pieces per row (dims nh*256 .. nh*256+255); one instruction serves two rows
+                                const int ql = lane & 15, sub = lane >> 4;
+                                const int q = nh * 16 + ql;
+                                const uint32_t dst0 = vring + slot * V_SLOT_BYTES + (ql >> 2) * BOX_BYTES + gw * 16 * 128;
+                                const int dslot = 2 * (ql & 3) + 1;
+#pragma unroll
+                                for (int u = 0; u < 8; ++u) {
+                                    const int rr = 2 * u + sub;
+                                    const uint8_t* r = shfl_ptr(rec, rr);
+                                    cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
+                                }
+                                cp_async_commit();
                             }
                         }
                     }
