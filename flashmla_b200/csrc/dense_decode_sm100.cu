@@ -58,6 +58,9 @@ constexpr int SIDE_BYTES = 144;               // per warp and tile: 32 rescale f
 constexpr int NTHREADS = 384;                 // dense mode: control warpgroup + two softmax / correction warpgroups
 constexpr int NTHREADS_GATHER = 512;          // sparse modes: one more warpgroup that gathers KV rows by index
 constexpr long long WAIT_LIMIT = 2000000000LL;    // SM cycles (about one second)
+#ifndef MLA_SLEEP_NS
+#define MLA_SLEEP_NS 200u
+#endif
 constexpr float RESCALE_THRESHOLD = 6.0f;         // log2 units
 
 // tensor-memory columns of the score CTA: two S accumulators and the first 7 chunks of Q
@@ -204,13 +207,14 @@ struct Walker<MODE_PREFILL> {
 struct Waiter {
     bool aborted = false;
     bool parked;                         // park the thread between probes instead of spinning
+    uint32_t sleep_ns;                   // ... and sleep this long between probes
     int* status;
     uint32_t* smem_flag;
-    __device__ Waiter(int* st, uint32_t* flag, bool park = false) : parked(park), status(st), smem_flag(flag) {}
+    __device__ Waiter(int* st, uint32_t* flag, bool park = false, uint32_t sleep = 0) : parked(park), sleep_ns(sleep), status(st), smem_flag(flag) {}
     template <bool CLUSTER>
     __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
         if (aborted) return;
-        const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT)
+        const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT, sleep_ns)
                                : mbar_wait_bounded<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT);
         if (!ok) {
             aborted = true;
@@ -268,6 +272,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t o[8];
+#ifdef MLA_DQ_BITS
+    // e4m3 bits placed into an fp32 word (the value times 2^-120, exact, sub-normals included), one multiply by
+    // scale * 2^120: the same product rounded once to fp32, without conversion instructions
+    const float scale120 = scale * 1.329227995784916e36f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float f[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const uint32_t x = __byte_perm(w[i], 0, 0x0444 | (b << 12));
+            f[b] = __uint_as_float((x & 0x80000000u) | ((x >> 4) & 0x07f00000u)) * scale120;
+        }
+        o[2 * i] = pack_bf16(f[0], f[1]);
+        o[2 * i + 1] = pack_bf16(f[2], f[3]);
+    }
+#else
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
@@ -277,6 +297,7 @@ __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& 
         o[2 * i] = pack_bf16(f0.x * scale, f0.y * scale);
         o[2 * i + 1] = pack_bf16(f1.x * scale, f1.y * scale);
     }
+#endif
     lo = make_uint4(o[0], o[1], o[2], o[3]);
     hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
@@ -337,7 +358,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
     const uint32_t tmem = sm.tmem_base;
     // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
-    Waiter wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12);
+    // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
+    Waiter wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
 
     // =====================================================================================================
