@@ -606,34 +606,35 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const uint32_t kring = smem_addr(sm.data + SC_KRING);
             const uint32_t vring = smem_addr(sm.data + VA_VRING);
             // converts K group `grp` (chunks 3grp..3grp+2; group 2 = chunks 6, 7 + RoPE chunk) for row `lane` of this warp
-            auto convert_k = [&](int grp, const float4& sc) {
+            // (The chunk loops below are deliberately not unrolled and the group index is a run-time value: with every
+            // instance unrolled the conversion code alone was several times the instruction cache, and the warps spent
+            // more time waiting for instructions than converting.)
+            auto convert_k = [&](const int grp, const float4& sc) {
                 const int rr = gw * 32 + lane, sw = rr & 7;
                 const int nconv = grp < 2 ? 3 : 2;
+#pragma unroll 1
+                for (int cj = 0; cj < nconv; ++cj) {
+                    const int j = grp * 3 + cj, sg = j >> 1;
+                    uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + rr * 128;
+                    const float scale = sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w;
+                    uint4 raw[4];
 #pragma unroll
-                for (int cj = 0; cj < 3; ++cj) {
-                    if (cj < nconv) {
-                        const int j = grp * 3 + cj;
-                        uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + rr * 128;
-                        const float scale = (j >> 1) == 0 ? sc.x : (j >> 1) == 1 ? sc.y : (j >> 1) == 2 ? sc.z : sc.w;
-                        uint4 raw[4];
+                    for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            uint4 lo, hi;
-                            dequant16(raw[k], scale, lo, hi);
-                            *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
-                            *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
-                        }
+                    for (int k = 0; k < 4; ++k) {
+                        uint4 lo, hi;
+                        dequant16(raw[k], scale, lo, hi);
+                        *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
+                        *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
                     }
                 }
             };
             // converts half of the 16 pieces of row (lane & 15) of this warp's 16 rows of V slot `slot` (dims nh*256..)
-            auto convert_v = [&](uint32_t slot, int nh, const float4& sc) {
+            auto convert_v = [&](const uint32_t slot, const int nh, const float4& sc) {
                 const int rr = gw * 16 + (lane & 15), sw = rr & 7, hb = lane >> 4;
                 const float s0 = nh ? sc.z : sc.x, s1 = nh ? sc.w : sc.y;
                 const float scale = hb ? s1 : s0;
-#pragma unroll
+#pragma unroll 1
                 for (int cj = 0; cj < 2; ++cj) {
                     uint8_t* rowp = sm.data + VA_VRING + slot * V_SLOT_BYTES + (hb * 2 + cj) * BOX_BYTES + rr * 128;
                     uint4 raw[4];
@@ -691,7 +692,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
                         const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
                         if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
-#pragma unroll
+#pragma unroll 1
                         for (int grp = 0; grp < 3; ++grp, ++ks, ++n_el) {
                             // first convert the element whose copies were issued two steps ago (one newer group of copies
                             // may still be in flight), so that the MMA warp works on it while this step's copies are issued
@@ -699,7 +700,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                                 cp_async_wait_group<1>();
                                 __syncwarp();
                                 GTRACE(3, n_el);
-                                const int pg = (grp + 1) % 3;                 // its group; it belongs to the previous tile unless grp == 2
+                                const int pg = grp == 2 ? 0 : grp + 1;        // its group; it belongs to the previous tile unless grp == 2
                                 convert_k(pg, grp == 2 ? sc_cur : sc_prev);
                                 publish(&sm.kv_full[pg]);
                             }
@@ -709,7 +710,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row.  A copy
                             // instruction costs the warp the same whatever its active lanes: each one serves two rows.
                             const int per_row = grp < 2 ? 12 : 16;
-                            const int sub = lane / per_row, ql = lane - sub * per_row;
+                            const int sub = grp < 2 ? (lane >= 12) + (lane >= 24) : lane >> 4, ql = lane - sub * per_row;
                             const bool active = sub < 2;
                             const bool is_rope = grp == 2 && ql >= 8;
                             const int q = grp * 12 + ql;                      // raw piece index in the row
@@ -734,7 +735,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     float4 sc_next = scales_of(rec_next);
                     int id_next = load_id(w.blk_begin + 1, tok);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
-#pragma unroll
+#pragma unroll 1
                         for (int h = 0; h < 2; ++h) {
                             const uint8_t* rec = rec_next;
                             sc_prev = sc_cur;
@@ -743,7 +744,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             rec_next = rec_of(nblk, id_next);
                             sc_next = scales_of(rec_next);
                             id_next = load_id(nblk + 1, tok);
-#pragma unroll
+#pragma unroll 1
                             for (int nh = 0; nh < 2; ++nh, ++ks, ++n_el) {
                                 if (n_el >= 2) {
                                     cp_async_wait_group<1>();
