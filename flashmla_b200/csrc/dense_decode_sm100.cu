@@ -687,11 +687,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         const uint8_t* rec = rec_next;
                         sc_prev = sc_cur;
                         sc_cur = sc_next;
+                        // (the fence comes before the prefetch loads are issued: it would wait for them)
+                        const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
+                        if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
                         rec_next = rec_of(myblk + 2 * (i + 1), id_next);
                         sc_next = scales_of(rec_next);
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
-                        const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
-                        if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
 #pragma unroll 1
                         for (int grp = 0; grp < 3; ++grp, ++ks, ++n_el) {
                             // first convert the element whose copies were issued two steps ago (one newer group of copies
@@ -799,10 +800,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 if (cta_rank == 0) {
                     // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
                     const int id = id_next;
-                    { const int posn = (i + 1) * 128 + gw * 32 + lane; id_next = posn < w.seqlen ? __ldg(idx + posn) : -1; }
                     const bool ok = id >= 0 && id < p.s_kv;
                     const uint32_t bal = __ballot_sync(0xffffffffu, ok);
                     if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }   // token 32w + l of the tile is bit l of word w
+                    // (issued after the fence, which would otherwise wait for it)
+                    { const int posn = (i + 1) * 128 + gw * 32 + lane; id_next = posn < w.seqlen ? __ldg(idx + posn) : -1; }
                     const int row_id = ok ? id : -1;
                     // A copy instruction costs the warp the same whatever its active lanes, so a token row (72 pieces of
                     // 16 bytes) is copied by two full-warp instructions (chunks 0-3, chunks 4-7) and the RoPE chunk of
