@@ -100,3 +100,37 @@ def test_serving_shape_sample():
         # convex combination of value rows, |out| is bounded by the largest |value| of the cache
         assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
         assert out.float().abs().max() <= d["blocked_k"].float().abs().max()
+
+
+def test_longcontext_shard_sample():
+    """Long-context sweep (1024 requests, log-normal lengths with median 8192, sigma 1, clipped to [256, 131072]):
+    the shard that one of eight GPUs gets (128 requests) runs in full; the longest, the shortest and three other
+    requests are checked against the oracle on their own pages, the whole shard through size-independent properties."""
+    from flashmla_b200 import workloads as W
+    import flashmla_b200 as fm
+    seq_all = W.seqlens_lognormal(1024, 8192, 1.0, 256, 131072, seed=0)
+    seq = seq_all[3 * 128:4 * 128].contiguous()
+    d = W.dense_decode_inputs(seq, 1, 128, 1, seed=11, device=DEV, data_on_device=True)
+    meta, _ = fm.get_mla_metadata()
+    out, lse = fm.flash_mla_with_kvcache(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], 512, meta, None, causal=True)
+    torch.cuda.synchronize()
+    fm.check_status()
+    order = torch.argsort(seq)
+    sample = sorted({int(order[0]), int(order[-1]), 5, 64, 127})
+    for i in sample:
+        n = int(seq[i])
+        pages = d["block_table"][i, :(n + 63) // 64].long()
+        kv_i = d["blocked_k"][pages].cpu()
+        bt_i = torch.arange(pages.numel(), dtype=torch.int32).view(1, -1)
+        ref_out, ref_lse = attention.dense_decode(d["q"][i:i + 1].cpu(), kv_i, bt_i, seq[i:i + 1], 512, True)
+        assert_out_close(f"out[{i}] (len {n})", out[i:i + 1], ref_out)
+        assert_lse_close(f"lse[{i}] (len {n})", lse[i:i + 1], ref_lse)
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    assert out.float().abs().max() <= d["blocked_k"].float().abs().max()
+    # the log-sum-exp of a longer prefix of the same keys can only grow: compare each request with its own first half
+    half = torch.clamp(seq // 2, min=1).to(DEV)
+    meta2, _ = fm.get_mla_metadata()
+    _, lse_half = fm.flash_mla_with_kvcache(d["q"], d["blocked_k"], d["block_table"], half, 512, meta2, None, causal=True)
+    torch.cuda.synchronize()
+    fm.check_status()
+    assert (lse >= lse_half - 1e-3).all()
