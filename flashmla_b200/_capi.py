@@ -87,6 +87,15 @@ class SparsePrefillArgs(Structure):
     ]
 
 
+class QuantizeArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_stride_block", c_int64), ("x_stride_row", c_int64),
+        ("num_blocks", c_int32), ("block_size", c_int32),
+        ("out", c_void_p), ("out_stride_block_bytes", c_int64),
+        ("pow2_scale", c_int32), ("_pad", c_int32), ("stream", c_void_p),
+    ]
+
+
 # every symbol include/flashmla_b200.h declares, with its signature
 SYMBOLS = {
     "mla_last_error": (c_char_p, []),
@@ -98,6 +107,7 @@ SYMBOLS = {
     "mla_combine": (c_int, [POINTER(CombineArgs)]),
     "mla_sparse_prefill_fwd": (c_int, [POINTER(SparsePrefillArgs)]),
     "mla_dense_decode_noalloc": (c_int, [POINTER(DenseDecodeArgs)]),
+    "mla_quantize_fp8_kvcache": (c_int, [POINTER(QuantizeArgs)]),
 }
 
 _lib = None

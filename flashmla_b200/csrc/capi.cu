@@ -171,4 +171,9 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* a) {
     return launch_sparse_prefill_portable(*a);
 }
 
+int mla_quantize_fp8_kvcache(const mla_quantize_args_t* a) {
+    MLA_CHECK_ARG(a != nullptr, "mla_quantize_fp8_kvcache: null argument struct");
+    return launch_quantize_fp8(*a);
+}
+
 }  // extern "C"

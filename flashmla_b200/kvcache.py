@@ -2,10 +2,13 @@
 
 Per token 656 bytes: 512 float8_e4m3fn "NoPE" values quantised per group of 128 with one fp32
 scale per group (x ~= fp8 * scale), the 4 scales, then 64 bf16 "RoPE" values stored as they are
-(layout: flash_mla/flash_mla_interface.py:92-98 of the reference).  Runs on whatever device the
-input lives on; it is a utility for producing caches, not part of the decode hot path.
+(layout: flash_mla/flash_mla_interface.py:92-98 of the reference).  CUDA tensors are quantised by the
+library's kernel (mla_quantize_fp8_kvcache); CPU tensors, which only tests and fixture generators pass,
+by the torch statement of the same arithmetic below.
 """
 import torch
+
+from . import _capi
 
 D_QK, D_NOPE, D_ROPE, GROUP, NUM_GROUPS = 576, 512, 64, 128, 4
 BYTES_PER_TOKEN = D_NOPE + 4 * NUM_GROUPS + 2 * D_ROPE
@@ -19,9 +22,19 @@ def quantize_fp8_kvcache(blocked_k: torch.Tensor, pow2_scale: bool = False, pad_
     every block, which makes the block stride differ from block_size * 656."""
     nb, bs, h_k, d = blocked_k.shape
     assert h_k == 1 and d == D_QK
+    assert blocked_k.dtype == torch.bfloat16
     x = blocked_k.squeeze(2)
     buf = torch.empty((nb, bs + pad_rows, BYTES_PER_TOKEN), dtype=torch.float8_e4m3fn, device=blocked_k.device)
     res = buf[:, :bs, :]
+    if blocked_k.is_cuda:
+        assert x.stride(-1) == 1, "the last dimension of blocked_k must be contiguous"
+        with torch.cuda.device(blocked_k.device):
+            args = _capi.QuantizeArgs(
+                x=_capi.ptr(x), x_stride_block=x.stride(0), x_stride_row=x.stride(1), num_blocks=nb, block_size=bs,
+                out=_capi.ptr(buf), out_stride_block_bytes=buf.stride(0), pow2_scale=1 if pow2_scale else 0,
+                stream=torch.cuda.current_stream().cuda_stream)
+            _capi.check(_capi.lib().mla_quantize_fp8_kvcache(args), "mla_quantize_fp8_kvcache")
+        return res.view(nb, bs, 1, BYTES_PER_TOKEN)
     grp = x[..., :D_NOPE].reshape(nb, bs, NUM_GROUPS, GROUP).float()
     scale = grp.abs().amax(dim=-1) / 448.0
     if pow2_scale:

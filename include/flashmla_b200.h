@@ -224,6 +224,24 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* args);
 #define MLA_NOALLOC_MAX_ROWS 16384
 int mla_dense_decode_noalloc(const mla_dense_decode_args_t* args);
 
+/* FP8 KV-cache writer (the step before sparse decode): bf16 token rows -> 656-byte records.  Replaces the torch
+ * quantiser the reference ships with its tests (tests/quant.py:20-53, quantize_k_cache, V32 layout; record layout
+ * flash_mla/flash_mla_interface.py:92-98): scale = amax/448 per group of 128 values (clamped to 1e-30), or with
+ * pow2_scale != 0 the smallest power of two >= max(amax/448, 1e-4); q = e4m3(x / scale).
+ * x: [num_blocks, block_size, 576] bf16 (strides in elements); out: [num_blocks, block_size, 656] bytes with a free
+ * block stride (>= block_size * 656, multiple of 16). */
+typedef struct {
+    const void* x;
+    int64_t x_stride_block, x_stride_row;
+    int32_t num_blocks, block_size;
+    void* out;
+    int64_t out_stride_block_bytes;
+    int32_t pow2_scale;
+    int32_t _pad;
+    void* stream;
+} mla_quantize_args_t;
+int mla_quantize_fp8_kvcache(const mla_quantize_args_t* args);
+
 #ifdef __cplusplus
 }
 #endif

@@ -166,3 +166,32 @@ def test_sparse_prefill_config4_rows():
     assert_out_close("out", out, ref[0])
     assert_lse_close("max_logits", mx, ref[1])
     assert_lse_close("lse", lse, ref[2])
+
+
+def test_fp8_cache_writer_bit_exact(golden_dir):
+    """The cache-write kernel against the oracle's quantiser, byte for byte: random rows at several magnitudes, an
+    all-zero row, padded block strides, both scale conventions, and the reference's own quantised bytes."""
+    from flashmla_b200.kvcache import quantize_fp8_kvcache
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(7, 64, 1, 576, generator=g)
+    x[1] *= 37.0
+    x[2] *= 1e-3
+    x[3, 5] = 0
+    x[4, :, :, 128:256] = 0
+    x = x.to(torch.bfloat16)
+    for pow2 in (False, True):
+        for pad in (0, 1):
+            ref = quant.quantize_v32(x, pow2_scale=pow2, pad_rows=pad)
+            got = quantize_fp8_kvcache(x.to(DEV), pow2_scale=pow2, pad_rows=pad)
+            assert got.stride(0) == (64 + pad) * 656
+            assert torch.equal(got.view(torch.uint8).contiguous().cpu(), ref.view(torch.uint8).contiguous()), (pow2, pad)
+    # non-contiguous input view (every other block of a larger cache)
+    big = torch.randn(6, 64, 1, 576, generator=g).to(torch.bfloat16)
+    view = big[::2]
+    dev_view = big.to(DEV)[::2]
+    assert torch.equal(quantize_fp8_kvcache(dev_view, False).view(torch.uint8).contiguous().cpu(),
+                       quant.quantize_v32(view, False, pad_rows=0).view(torch.uint8).contiguous())
+    c = torch.load(os.path.join(golden_dir, "quant_v32.pt"), weights_only=False)
+    got = quantize_fp8_kvcache(c["x"].to(DEV), pow2_scale=True, pad_rows=1)
+    assert got.stride(0) == c["quant_stride0"]
+    assert torch.equal(got.view(torch.uint8).contiguous().cpu().reshape(-1), c["quant_bytes"].reshape(-1))
