@@ -32,6 +32,25 @@ D_QK, D_V = 576, 512
 # workloads: inputs + algorithmic bytes / flops (conventions of the reference's own test scripts:
 # tests/test_flash_mla_dense_decoding.py:174-190, tests/lib.py:345-402)
 # ------------------------------------------------------------------------------------------------------
+def shard_of_rank(n_total, world, rank):
+    """Requests [begin, end) of the batch-sharded sweep that `rank` of `world` serves (equal shares, no overlap)."""
+    per = n_total // world
+    return rank * per, (rank + 1) * per
+
+
+def reduce_over_ranks(ms_total, ms_e2e_total, units, tokens, flops, nbytes, dist, device):
+    """Whole-job figures from per-rank ones: times are the MAXIMUM over ranks (the job is as slow as its slowest
+    rank), work is the SUM.  `dist` is torch.distributed (any backend) or None for a single process."""
+    if dist is None:
+        return ms_total, ms_e2e_total, units, tokens, flops, nbytes
+    stats = torch.tensor([ms_total, ms_e2e_total, units, tokens, flops, nbytes], dtype=torch.float64, device=device)
+    mx = stats.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    sm = stats.clone()
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    return float(mx[0]), float(mx[1]), float(sm[2]), float(sm[3]), float(sm[4]), float(sm[5])
+
+
 def make_workload(name, device, seed, prefill_sq=4096):
     from flashmla_b200 import workloads as W
     if name in ("dense", "dense_sq2"):
@@ -49,8 +68,9 @@ def make_workload(name, device, seed, prefill_sq=4096):
         world = int(os.environ.get("WORLD_SIZE", "1"))
         rank = int(os.environ.get("RANK", "0"))
         seq_all = W.seqlens_lognormal(b_total, 8192, 1.0, 256, 131072, seed=0)
-        per = b_total // world
-        seq = seq_all[rank * per:(rank + 1) * per].contiguous()
+        begin, end = shard_of_rank(b_total, world, rank)
+        per = end - begin
+        seq = seq_all[begin:end].contiguous()
         d = W.dense_decode_inputs(seq, 1, h_q, 1, seed=seed, device=device, data_on_device=True)
         S = int(seq.sum())
         return dict(kind="dense", inputs=d, s_q=1, b=per, h_q=h_q, tokens=S,
@@ -443,17 +463,8 @@ def main():
         raise SystemExit("bench.py: the end-to-end leg returned a different result than the device-resident leg")
 
     # ---- reduce over ranks ---------------------------------------------------------------------------------
-    stats = torch.tensor([ms_total, ms_e2e_total, units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"])],
-                         dtype=torch.float64, device=dev)
-    if dist is not None:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        ms_total, ms_e2e_total = float(mx[0]), float(mx[1])
-        units_all, tokens_all, flops_all, bytes_all = float(sm[2]), float(sm[3]), float(sm[4]), float(sm[5])
-    else:
-        units_all, tokens_all, flops_all, bytes_all = units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"])
+    ms_total, ms_e2e_total, units_all, tokens_all, flops_all, bytes_all = reduce_over_ranks(
+        ms_total, ms_e2e_total, units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"]), dist, dev)
     if rank != 0:
         dist.destroy_process_group()
         return
