@@ -82,8 +82,9 @@ int mla_num_sm_parts(int device, int mode, int h_q, int h_kv, int s_q) {
         int p = sms / 2 / h_kv / row_blocks;
         return p > 0 ? p : 1;
     } else if (mode == MLA_MODE_SPARSE_DECODE) {
-        const int row_blocks = (h_q + 63) / 64;
-        int p = sms / s_q / row_blocks;
+        // up to 128 heads: one CTA pair of the tcgen05 kernel per partition and query token; more heads run on the
+        // portable kernel, one CTA per 64 heads
+        int p = h_q <= 128 ? sms / 2 / s_q : sms / s_q / ((h_q + 63) / 64);
         return p > 0 ? p : 1;
     }
     set_error(MLA_ERR_INVALID_ARG, "mla_num_sm_parts: unknown mode %d", mode);
@@ -146,8 +147,9 @@ int mla_sparse_decode_fwd(const mla_sparse_decode_args_t* a) {
             return set_error(MLA_ERR_UNSUPPORTED, "mla_sparse_decode_fwd: the tcgen05 kernel does not support this shape");
         return launch_sparse_decode_sm100(*a);
     }
-    // the tcgen05 kernel works on blocks of 128 rows: with 64 heads or fewer the portable kernel wastes less
-    if (a->impl == 0 && a->h_q > 64 && sparse_decode_sm100_supports(*a)) return launch_sparse_decode_sm100(*a);
+    // (also with few heads: the work is dominated by gathering and de-quantising the records, which the tcgen05
+    // kernel does 2x faster than the portable one even when most of its 128 rows are padding)
+    if (a->impl == 0 && sparse_decode_sm100_supports(*a)) return launch_sparse_decode_sm100(*a);
     return launch_sparse_decode_portable(*a);
 }
 
