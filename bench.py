@@ -441,9 +441,32 @@ def main():
         e1.record()
         barrier()
         fmi.set_kernel_timer(None)
-    ms_total = e0.elapsed_time(e1)
+    ms_eager = e0.elapsed_time(e1)
     kernel_ms = timer.mean_ms()
     launches = timer.launches()
+
+    # ---- the same steps as a CUDA graph: one step is captured once and replayed (a decode loop is launch-bound between
+    # its kernels; the API neither allocates outside torch's allocator nor synchronises, so it can be captured) --------
+    ms_total, launch_mode = ms_eager, "eager launches"
+    try:
+        eager_out, eager_lse = run_step(w)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            g_out, g_lse = run_step(w)
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            barrier()
+        if not (torch.equal(g_out.view(torch.int16), eager_out.view(torch.int16)) and torch.equal(g_lse, eager_lse)):
+            raise RuntimeError("graph replay and eager launch disagree")
+        ms_total, launch_mode = e0.elapsed_time(e1), "CUDA graph replay of one step"
+    except Exception as exc:                      # capture is an optimisation of the launch path, never a requirement
+        print(f"bench.py: CUDA graph capture not used ({exc})", file=sys.stderr)
 
     # ---- end-to-end timing: host buffers in, result out --------------------------------------------------
     host, h2d, d2h = make_host_buffers(w)
@@ -493,7 +516,8 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": "inputs larger than L2 (KV cache streamed once per step)",
-                   "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel]},
+                   "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel], "launch": launch_mode},
+        "ms_per_step_eager": ms_eager / args.steps,
         "tflops": flops_all / 1e12 / (ms_step / 1e3), "hbm_gbs": bytes_all / 1e9 / (ms_step / 1e3),
         "kv_tokens_per_s": tokens_all / (ms_step / 1e3),
         "kernel_ms": kernel_ms, "gpu_launches": launches,
