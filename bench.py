@@ -513,7 +513,8 @@ def main():
 
     line = {
         "metric": metric, "value": units_all / (ms_step / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "longctx" else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": "inputs larger than L2 (KV cache streamed once per step)",
                    "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel], "launch": launch_mode},
