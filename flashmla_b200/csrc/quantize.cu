@@ -70,7 +70,7 @@ int launch_quantize_fp8(const mla_quantize_args_t& a) {
     const int64_t ntok = (int64_t)a.num_blocks * a.block_size;
     const int sms = current_device_num_sms();
     int64_t blocks = (ntok + 7) / 8;
-    const int64_t cap = (int64_t)(sms > 0 ? sms : 148) * 16;
+    const int64_t cap = (int64_t)(sms > 0 ? sms : 148) * 32;
     if (blocks > cap) blocks = cap;
     quantize_fp8_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)a.stream>>>(a);
     MLA_CHECK_CUDA(cudaGetLastError());
