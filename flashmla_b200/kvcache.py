@@ -45,3 +45,30 @@ def quantize_fp8_kvcache(blocked_k: torch.Tensor, pow2_scale: bool = False, pad_
     res[..., D_NOPE:D_NOPE + 4 * NUM_GROUPS].view(torch.float32)[:] = scale
     res[..., D_NOPE + 4 * NUM_GROUPS:].view(torch.bfloat16)[:] = x[..., D_NOPE:]
     return res.view(nb, bs, 1, BYTES_PER_TOKEN)
+
+
+if __name__ == "__main__":
+    # python -m flashmla_b200.kvcache [--blocks N]: times the cache-write kernel on N blocks of 64 random bf16 rows
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--blocks", type=int, default=32768)
+    ap.add_argument("--steps", type=int, default=10)
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("needs a CUDA device (there is no CPU path)")
+    x = torch.randn(a.blocks, 64, 1, D_QK, device="cuda", dtype=torch.bfloat16)
+    for _ in range(3):
+        quantize_fp8_kvcache(x)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(a.steps):
+        quantize_fp8_kvcache(x)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / a.steps
+    ntok = a.blocks * 64
+    print(json.dumps({"kernel": "quantize_fp8_kernel", "tokens": ntok, "ms": ms,
+                      "gbs": ntok * (2 * D_QK + BYTES_PER_TOKEN) / ms / 1e6, "bytes_per_token": 2 * D_QK + BYTES_PER_TOKEN}))
