@@ -88,6 +88,7 @@ struct Smem {
     uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
     uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
+    uint64_t raw_full[3];                // score CTA, FP8 decode: the raw records of a ring group have landed
     uint32_t tmem_base;
     uint32_t aborted;
 };
@@ -117,7 +118,8 @@ struct Params {
 enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
 constexpr int SC_MASK = SC_END;          // score CTA, prefill: validity bits of the last 4 tiles, [4][4] words
 constexpr int SC_LSUM = SC_MASK + 64;    // score CTA: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
-static_assert(SC_LSUM + ROWS * 4 <= DATA_BYTES, "score CTA scratch must fit");
+constexpr int SC_SCALES = SC_LSUM + ROWS * 4;   // score CTA, FP8 decode: the 4 scales of every token of the last two tiles, [2][128] float4
+static_assert(SC_SCALES + 2 * ROWS * 16 <= DATA_BYTES, "score CTA scratch must fit");
 
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
@@ -327,7 +329,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     if (threadIdx.x == 0) {
         // a ring slot is filled by TMA (one arrive.expect_tx + bytes) in dense mode, by the 128 gather threads otherwise
-        for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), MODE == MODE_DENSE ? 1 : 128); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
+        // ... except the K groups of FP8 decode, which the 256 softmax threads of the score CTA hand over after de-quantising them
+        const uint32_t full_count = MODE == MODE_DENSE ? 1 : (MODE == MODE_SPARSE_DECODE && cta_rank == 0) ? 256 : 128;
+        for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), full_count); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
+        for (int i = 0; i < 3; ++i) mbar_init(smem_addr(&sm.raw_full[i]), 128);
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.s_full[i]), 1);
             mbar_init(smem_addr(&sm.s_empty[i]), 256);
@@ -606,29 +611,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const uint32_t kring = smem_addr(sm.data + SC_KRING);
             const uint32_t vring = smem_addr(sm.data + VA_VRING);
             // converts K group `grp` (chunks 3grp..3grp+2; group 2 = chunks 6, 7 + RoPE chunk) for row `lane` of this warp
-            // (The chunk loops below are deliberately not unrolled and the group index is a run-time value: with every
-            // instance unrolled the conversion code alone was several times the instruction cache, and the warps spent
-            // more time waiting for instructions than converting.)
-            auto convert_k = [&](const int grp, const float4& sc) {
-                const int rr = gw * 32 + lane, sw = rr & 7;
-                const int nconv = grp < 2 ? 3 : 2;
-#pragma unroll 1
-                for (int cj = 0; cj < nconv; ++cj) {
-                    const int j = grp * 3 + cj, sg = j >> 1;
-                    uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + rr * 128;
-                    const float scale = sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w;
-                    uint4 raw[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint4 lo, hi;
-                        dequant16(raw[k], scale, lo, hi);
-                        *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
-                        *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
-                    }
-                }
-            };
+            // (The chunk loops below are deliberately not unrolled: with every instance unrolled the conversion code alone
+            // was several times the instruction cache, and the warps spent more time waiting for instructions than
+            // converting.)  In the score CTA the gather warps only copy; the softmax warpgroups, idle most of a tile's
+            // time in this mode, expand the pieces.
             // converts half of the 16 pieces of row (lane & 15) of this warp's 16 rows of V slot `slot` (dims nh*256..)
             auto convert_v = [&](const uint32_t slot, const int nh, const float4& sc) {
                 const int rr = gw * 16 + (lane & 15), sw = rr & 7, hb = lane >> 4;
@@ -685,29 +671,21 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     int id_next = load_id(myblk + 2, tok & 63);              // tile 1
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         const uint8_t* rec = rec_next;
-                        sc_prev = sc_cur;
                         sc_cur = sc_next;
-                        // (the fence comes before the prefetch loads are issued: it would wait for them)
+                        // validity bits and scales of this tile's tokens for the threads that convert / mask it (the fence
+                        // comes before the prefetch loads are issued: it would wait for them)
                         const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
-                        if (lane == 0) { kmask[(g & 3) * 4 + gw] = bal; __threadfence_block(); }
+                        if (lane == 0) kmask[(g & 3) * 4 + gw] = bal;
+                        reinterpret_cast<float4*>(sm.data + SC_SCALES)[(g & 1) * ROWS + tok] = sc_cur;
+                        __threadfence_block();
                         rec_next = rec_of(myblk + 2 * (i + 1), id_next);
                         sc_next = scales_of(rec_next);
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
 #pragma unroll 1
-                        for (int grp = 0; grp < 3; ++grp, ++ks, ++n_el) {
-                            // first convert the element whose copies were issued two steps ago (one newer group of copies
-                            // may still be in flight), so that the MMA warp works on it while this step's copies are issued
-                            if (n_el >= 2) {
-                                cp_async_wait_group<1>();
-                                __syncwarp();
-                                GTRACE(3, n_el);
-                                const int pg = grp == 2 ? 0 : grp + 1;        // its group; it belongs to the previous tile unless grp == 2
-                                convert_k(pg, grp == 2 ? sc_cur : sc_prev);
-                                publish(&sm.kv_full[pg]);
-                            }
-                            GTRACE(0, n_el);
+                        for (int grp = 0; grp < 3; ++grp, ++ks) {
+                            GTRACE(0, ks);
                             wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                            GTRACE(1, n_el);
+                            GTRACE(1, ks);
                             // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row.  A copy
                             // instruction costs the warp the same whatever its active lanes: each one serves two rows.
                             const int per_row = grp < 2 ? 12 : 16;
@@ -725,8 +703,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                                 if (active)
                                     cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + srcoff, r ? 16u : 0u);
                             }
-                            cp_async_commit();
-                            GTRACE(2, n_el);
+                            // the softmax warpgroups expand the pieces in place once they have landed
+                            cp_async_arrive_noinc(smem_addr(&sm.raw_full[grp]));
+                            GTRACE(2, ks);
                         }
                     }
                 } else {
@@ -778,14 +757,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             if (n_el >= 2) {
                 cp_async_wait_group<1>();
                 __syncwarp();
-                if (cta_rank == 0) { convert_k(1, sc_cur); publish(&sm.kv_full[1]); }
-                else { const uint32_t pslot = (ks - 2) % NVS; convert_v(pslot, 0, sc_cur); publish(&sm.kv_full[pslot]); }
+                if (cta_rank == 1) { const uint32_t pslot = (ks - 2) % NVS; convert_v(pslot, 0, sc_cur); publish(&sm.kv_full[pslot]); }
             }
             if (n_el >= 1) {
                 cp_async_wait_group<0>();
                 __syncwarp();
-                if (cta_rank == 0) { convert_k(2, sc_cur); publish(&sm.kv_full[2]); }
-                else { const uint32_t pslot = (ks - 1) % NVS; convert_v(pslot, 1, sc_cur); publish(&sm.kv_full[pslot]); }
+                if (cta_rank == 1) { const uint32_t pslot = (ks - 1) % NVS; convert_v(pslot, 1, sc_cur); publish(&sm.kv_full[pslot]); }
             }
         } else
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -896,6 +873,43 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const uint32_t remote_fin_m = map_to_cta(smem_addr(&sm.fin_m[r]), 1);
             const uint32_t remote_fin_mt = map_to_cta(smem_addr(&sm.fin_mt[r]), 1);
             const uint32_t remote_fin_full = map_to_cta(smem_addr(&sm.fin_full), 1);
+            // FP8 decode: these 256 threads also de-quantise the K tiles in place (two threads per token row, every other
+            // 16-value piece each), one tile ahead of the softmax they compute: tile g + 1 is converted before the scores
+            // of tile g are awaited, so the MMA warp has the next tile while this warpgroup is busy with the softmax.
+            uint32_t total_tiles = 0, conv_tile = 0;
+            if (MODE == MODE_SPARSE_DECODE)
+                for (WalkerT w2(p, part); w2.valid(); w2.next()) total_tiles += w2.get().ntiles;
+            Waiter wt_fast(p.status, &sm.aborted);                   // conversion sits on the MMA warp's critical path: no sleeping
+            auto convert_tile = [&](const uint32_t tile) {
+                const int sw = r & 7;
+                float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int grp = 0; grp < 3; ++grp) {
+                    wt_fast.wait<false>(&sm.raw_full[grp], tile & 1, 205);
+                    // the tile's scales were stored (and fenced) by the gather warps before they issued its first copies
+                    if (grp == 0) sc = reinterpret_cast<const float4*>(sm.data + SC_SCALES)[(tile & 1) * ROWS + r];
+                    const int nconv = grp < 2 ? 3 : 2;                 // group 2: chunks 6, 7 and the RoPE chunk (copied as it is)
+#pragma unroll 1
+                    for (int cj = 0; cj < nconv; ++cj) {
+                        const int j = grp * 3 + cj, sg = j >> 1;
+                        uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + r * 128;
+                        const float scale = sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w;
+                        uint4 raw[2];
+#pragma unroll
+                        for (int k2 = 0; k2 < 2; ++k2) raw[k2] = *reinterpret_cast<const uint4*>(rowp + (((2 * (half + 2 * k2) + 1) ^ sw) << 4));
+#pragma unroll
+                        for (int k2 = 0; k2 < 2; ++k2) {
+                            const int k = half + 2 * k2;
+                            uint4 lo, hi;
+                            dequant16(raw[k2], scale, lo, hi);
+                            *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
+                            *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
+                        }
+                    }
+                    fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's reads
+                    mbar_arrive(smem_addr(&sm.kv_full[grp]));
+                }
+            };
             for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
                 // ---- Q row -> A operand: chunks 0..6 to tensor memory (2 bf16 per 32-bit column), chunks 7, 8 to shared
@@ -940,6 +954,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t sb = g & 1, ph = (g >> 1) & 1;
+                    if (MODE == MODE_SPARSE_DECODE)
+                        while (conv_tile <= g + 1 && conv_tile < total_tiles) convert_tile(conv_tile++);
                     wt.wait<false>(&sm.s_full[sb], ph, 5);
                     tc_fence_after();
                     if (threadIdx.x == 128) TRACE(3, g);
