@@ -88,7 +88,7 @@ struct Smem {
     uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
     uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
-    uint64_t raw_full[3];                // score CTA, FP8 decode: the raw records of a ring group have landed
+    uint64_t raw_full[NRING];            // FP8 decode: the raw records of a K group (score CTA) / V slot (value CTA) have landed
     uint32_t tmem_base;
     uint32_t aborted;
 };
@@ -332,7 +332,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // ... except the K groups of FP8 decode, which the 256 softmax threads of the score CTA hand over after de-quantising them
         const uint32_t full_count = MODE == MODE_DENSE ? 1 : (MODE == MODE_SPARSE_DECODE && cta_rank == 0) ? 256 : 128;
         for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), full_count); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
-        for (int i = 0; i < 3; ++i) mbar_init(smem_addr(&sm.raw_full[i]), 128);
+        for (int i = 0; i < NRING; ++i) mbar_init(smem_addr(&sm.raw_full[i]), 128);
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_addr(&sm.s_full[i]), 1);
             mbar_init(smem_addr(&sm.s_empty[i]), 256);
@@ -596,50 +596,21 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // A "piece" is 16 e4m3 values (16 bytes) that de-quantise (one rounding: bf16(fp32(e4m3) * scale)) into two
             // 16-byte slots of a 128-byte operand row.  Two decoupled steps per ring element (a K group of 3 chunks in
             // the score CTA, a V slot of 4 chunks in the value CTA):
-            //   copy:    cp.async brings every raw piece straight into the UPPER of its own two destination slots (one
-            //            instruction per token row, lanes = pieces: coalesced, no registers held), RoPE pieces into
-            //            their final place;
-            //   convert: two elements later, when the copies have landed, every lane expands the pieces of its own
-            //            row in place (it reads a slot only it will overwrite; 16-byte accesses, conflict-free thanks
-            //            to the swizzle) and the element is handed to the tensor core.
-            // The element's copies are in flight while the two elements before it are converted: that is what covers
-            // the latency of the scattered record reads.  Record pointers and scales of the next tile are fetched
-            // while the current one is processed.
+            //   copy:    this warpgroup brings every raw piece with cp.async straight into the UPPER of its own two
+            //            destination slots (lanes = pieces of two token rows: coalesced, no registers held), RoPE pieces
+            //            into their final place, and counts the landing on the element's raw_full barrier;
+            //   convert: warps that are idle most of a tile's time in this mode - the softmax warpgroups of the score
+            //            CTA, warps 8-11 of the value CTA - expand the pieces of their token row in place (a thread reads
+            //            a slot only it will overwrite; 16-byte accesses, conflict-free thanks to the swizzle) and hand
+            //            the element to the MMA warp.
+            // Copying and converting run side by side on different warps; record pointers (and, in the score CTA, the
+            // scales the converting threads read from shared memory) are fetched one tile ahead.  The conversion loops
+            // are deliberately left rolled: with every instance unrolled the conversion code was several times the
+            // instruction cache and the warps waited for instructions more than they computed.
             const int tq = blockIdx.y;
-            uint32_t n_el = 0;                               // elements issued so far (all requests of this CTA)
-            float4 sc_cur = make_float4(0.f, 0.f, 0.f, 0.f), sc_prev = sc_cur;
+            float4 sc_cur = make_float4(0.f, 0.f, 0.f, 0.f);
             const uint32_t kring = smem_addr(sm.data + SC_KRING);
             const uint32_t vring = smem_addr(sm.data + VA_VRING);
-            // converts K group `grp` (chunks 3grp..3grp+2; group 2 = chunks 6, 7 + RoPE chunk) for row `lane` of this warp
-            // (The chunk loops below are deliberately not unrolled: with every instance unrolled the conversion code alone
-            // was several times the instruction cache, and the warps spent more time waiting for instructions than
-            // converting.)  In the score CTA the gather warps only copy; the softmax warpgroups, idle most of a tile's
-            // time in this mode, expand the pieces.
-            // converts half of the 16 pieces of row (lane & 15) of this warp's 16 rows of V slot `slot` (dims nh*256..)
-            auto convert_v = [&](const uint32_t slot, const int nh, const float4& sc) {
-                const int rr = gw * 16 + (lane & 15), sw = rr & 7, hb = lane >> 4;
-                const float s0 = nh ? sc.z : sc.x, s1 = nh ? sc.w : sc.y;
-                const float scale = hb ? s1 : s0;
-#pragma unroll 1
-                for (int cj = 0; cj < 2; ++cj) {
-                    uint8_t* rowp = sm.data + VA_VRING + slot * V_SLOT_BYTES + (hb * 2 + cj) * BOX_BYTES + rr * 128;
-                    uint4 raw[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint4 lo, hi;
-                        dequant16(raw[k], scale, lo, hi);
-                        *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
-                        *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
-                    }
-                }
-            };
-            // hands element e (already converted by this thread) to the MMA warp
-            auto publish = [&](uint64_t* bar) {
-                fence_proxy_async_smem();              // generic-proxy stores -> visible to the tensor core's reads
-                mbar_arrive(smem_addr(bar));
-            };
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
@@ -712,28 +683,16 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     // value CTA: warp gw owns tokens 16*gw .. 16*gw+15 of each page; lanes l and l + 16 look up the same token
                     const int tok = gw * 16 + (lane & 15);
                     const uint8_t* rec_next = rec_of(w.blk_begin, load_id(w.blk_begin, tok));
-                    float4 sc_next = scales_of(rec_next);
                     int id_next = load_id(w.blk_begin + 1, tok);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
 #pragma unroll 1
                         for (int h = 0; h < 2; ++h) {
                             const uint8_t* rec = rec_next;
-                            sc_prev = sc_cur;
-                            sc_cur = sc_next;
                             const int nblk = w.blk_begin + 2 * i + h + 1;
                             rec_next = rec_of(nblk, id_next);
-                            sc_next = scales_of(rec_next);
                             id_next = load_id(nblk + 1, tok);
 #pragma unroll 1
-                            for (int nh = 0; nh < 2; ++nh, ++ks, ++n_el) {
-                                if (n_el >= 2) {
-                                    cp_async_wait_group<1>();
-                                    __syncwarp();
-                                    // the element two steps back: same page if nh == 1 ... (h, nh) -> (h - 1, nh) in slot order
-                                    const uint32_t pslot = (ks - 2) % NVS;
-                                    convert_v(pslot, nh, sc_prev);
-                                    publish(&sm.kv_full[pslot]);
-                                }
+                            for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
                                 wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
                                 // copy: 16 raw pieces per row (dims nh*256 .. nh*256+255); one instruction serves two rows
@@ -747,22 +706,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                                     const uint8_t* r = shfl_ptr(rec, rr);
                                     cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
                                 }
-                                cp_async_commit();
+                                cp_async_arrive_noinc(smem_addr(&sm.raw_full[slot]));      // warps 8-11 expand the pieces
                             }
                         }
                     }
                 }
-            }
-            // drain: the last two elements
-            if (n_el >= 2) {
-                cp_async_wait_group<1>();
-                __syncwarp();
-                if (cta_rank == 1) { const uint32_t pslot = (ks - 2) % NVS; convert_v(pslot, 0, sc_cur); publish(&sm.kv_full[pslot]); }
-            }
-            if (n_el >= 1) {
-                cp_async_wait_group<0>();
-                __syncwarp();
-                if (cta_rank == 1) { const uint32_t pslot = (ks - 1) % NVS; convert_v(pslot, 1, sc_cur); publish(&sm.kv_full[pslot]); }
             }
         } else
         for (WalkerT wk(p, part); wk.valid(); wk.next()) {
@@ -1179,6 +1127,66 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 tc_fence_before();
                 if (threadIdx.x == 128) SPAN(5, nreq);
                 mbar_arrive_remote(remote_fin_empty);        // fin_l / fin_m may be rewritten
+            }
+        } else if (MODE == MODE_SPARSE_DECODE) {
+            // ---------------- value CTA, FP8 decode: warps 8-11 de-quantise the V slots in place ------------------
+            // Thread = (token row of the page, half of the slot's four chunks).  It looks up its token's record by
+            // itself, one page ahead, for the two scales it needs; the raw pieces were copied by the gather warpgroup.
+            const int trow = r & 63, hb = r >> 6, sw = trow & 7;
+            const int tq = blockIdx.y;
+            uint32_t ks = 0;
+            Waiter wt_fast(p.status, &sm.aborted);               // this sits on the MMA warp's critical path: no sleeping
+            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+                const Work w = wk.get();
+                const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
+                const int* idx1 = p.stopk[1] ? p.sidx[1] + (int64_t)w.req * p.sidx_sb[1] + (int64_t)tq * p.sidx_ss[1] : nullptr;
+                auto load_id = [&](int blk) -> int {
+                    if (blk >= w.blk_end) return -1;
+                    const int scope = blk >= w.nblk0 ? 1 : 0;
+                    const int pos = (scope ? blk - w.nblk0 : blk) * PAGE + trow;
+                    if (pos >= (scope ? w.len1 : w.len0)) return -1;
+                    return __ldg((scope ? idx1 : idx0) + pos);
+                };
+                auto scales_of_id = [&](int blk, int id) -> float4 {
+                    const int scope = blk >= w.nblk0 ? 1 : 0;
+                    const int pbs = p.pbs[scope];
+                    if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return make_float4(0.f, 0.f, 0.f, 0.f);
+                    return __ldg(reinterpret_cast<const float4*>(p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] +
+                                                                 (int64_t)(id % pbs) * 656 + 512));
+                };
+                float4 sc_next = scales_of_id(w.blk_begin, load_id(w.blk_begin));
+                int id_next = load_id(w.blk_begin + 1);
+                for (int i = 0; i < w.ntiles; ++i) {
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        const float4 sc = sc_next;
+                        const int nblk = w.blk_begin + 2 * i + h + 1;
+                        sc_next = scales_of_id(nblk, id_next);
+                        id_next = load_id(nblk + 1);
+#pragma unroll 1
+                        for (int nh = 0; nh < 2; ++nh, ++ks) {
+                            const uint32_t slot = ks % NVS;
+                            wt_fast.wait<false>(&sm.raw_full[slot], (ks / NVS) & 1, 206);
+                            const float scale = hb ? (nh ? sc.w : sc.y) : (nh ? sc.z : sc.x);
+#pragma unroll 1
+                            for (int cj = 0; cj < 2; ++cj) {
+                                uint8_t* rowp = sm.data + VA_VRING + slot * V_SLOT_BYTES + (hb * 2 + cj) * BOX_BYTES + trow * 128;
+                                uint4 raw[4];
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) raw[k] = *reinterpret_cast<const uint4*>(rowp + (((2 * k + 1) ^ sw) << 4));
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    uint4 lo, hi;
+                                    dequant16(raw[k], scale, lo, hi);
+                                    *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
+                                    *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
+                                }
+                            }
+                            fence_proxy_async_smem();              // generic-proxy stores -> visible to the tensor core's reads
+                            mbar_arrive(smem_addr(&sm.kv_full[slot]));
+                        }
+                    }
+                }
             }
         }
     }
