@@ -101,6 +101,7 @@ SYMBOLS = {
     "mla_last_error": (c_char_p, []),
     "mla_abi_version": (c_int, []),
     "mla_num_sm_parts": (c_int, [c_int, c_int, c_int, c_int, c_int]),
+    "mla_num_sm_parts_uniform": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "mla_get_sched_meta": (c_int, [POINTER(SchedMetaArgs)]),
     "mla_dense_decode_fwd": (c_int, [POINTER(DenseDecodeArgs)]),
     "mla_sparse_decode_fwd": (c_int, [POINTER(SparseDecodeArgs)]),

@@ -91,6 +91,24 @@ int mla_num_sm_parts(int device, int mode, int h_q, int h_kv, int s_q) {
     return -1;
 }
 
+int mla_num_sm_parts_uniform(int device, int mode, int h_q, int h_kv, int s_q, int b, int blocks_per_request) {
+    const int p = mla_num_sm_parts(device, mode, h_q, h_kv, s_q);
+    if (p <= 0) return p;
+    if (b <= 0 || blocks_per_request <= 0) {
+        set_error(MLA_ERR_INVALID_ARG, "mla_num_sm_parts_uniform: batch size and blocks per request must be positive");
+        return -1;
+    }
+    if (b > p) return p;
+    // Every request costs the same, so the greedy scheduler cuts a multiple of b partitions exactly at request
+    // boundaries: no partition then walks two requests (one Q load and one epilogue each instead of two) and, with
+    // one partition per request, nothing is left to combine.  That leaves p - k*b CTA pairs idle; take it when the
+    // extra blocks per partition cost less than the boundary they save (about 8 blocks of 64 tokens, measured).
+    const int k = p / b;
+    const double blocks_even = (double)blocks_per_request / k;
+    const double blocks_greedy = (double)blocks_per_request * b / p;
+    return (blocks_even - blocks_greedy) < 8.0 ? k * b : p;
+}
+
 int mla_get_sched_meta(const mla_sched_meta_args_t* a) {
     MLA_CHECK_ARG(a != nullptr, "mla_get_sched_meta: null argument struct");
     return launch_sched_meta(*a);

@@ -60,6 +60,12 @@ int mla_abi_version(void);
  * (csrc/api/sparse_decode.h:92-99,126-133).  Returns <= 0 on error. */
 int mla_num_sm_parts(int device, int mode, int h_q, int h_kv, int s_q);
 
+/* Same, for a batch of `b` requests that all cost `blocks_per_request` KV blocks of 64 tokens (sparse decode with a
+ * fixed top-k and no per-request lengths; the reference derives its partition count from the SM count alone at
+ * csrc/api/sparse_decode.h:92-99).  May return fewer partitions than mla_num_sm_parts so that no partition
+ * straddles two requests.  Deterministic in its arguments: callers that cache metadata get the same count back. */
+int mla_num_sm_parts_uniform(int device, int mode, int h_q, int h_kv, int s_q, int b, int blocks_per_request);
+
 /* Tile-scheduler metadata.  Replaces run_get_decoding_sched_meta_kernel
  * (csrc/smxx/decode/get_decoding_sched_meta/get_decoding_sched_meta.cu:109-114);
  * arguments mirror GetDecodeSchedMetaParams (csrc/params.h:127-143). */

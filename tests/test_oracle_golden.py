@@ -67,3 +67,15 @@ def test_sparse_prefill_oracle_matches_reference(golden_dir):
         assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
         assert check_close("max_logits", mx, c["max_logits"], abs_tol=2e-6, rel_tol=1e-6)
         assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
+
+
+def test_uniform_costs_one_partition_per_request_never_split():
+    """With equal request costs and as many partitions as requests the greedy scheduler cuts at every request boundary
+    (the sparse decode path relies on this to skip the combine kernel)."""
+    for b in (1, 2, 7, 64, 74):
+        for topk in (1, 64, 128, 2048, 2049):
+            for extra in (-1, 64, 512):
+                meta, ns = sched_meta.get_sched_meta(b, b, 64, 5, topk=topk, extra_topk=extra)
+                assert ns.tolist() == list(range(b + 1)), (b, topk, extra)
+                assert meta[:, 0].tolist() == list(range(b)) and meta[:, 1].tolist() == list(range(b))
+                assert not meta[:, 5].any() and not meta[:, 6].any()
