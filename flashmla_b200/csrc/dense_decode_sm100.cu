@@ -88,6 +88,7 @@ struct Smem {
     uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
     uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
+    uint64_t q_landed, ring_released;    // score CTA: the first request's Q boxes have landed / have been copied out of the K ring
     uint64_t raw_full[NRING];            // FP8 decode: the raw records of a K group (score CTA) / V slot (value CTA) have landed
     uint32_t tmem_base;
     uint32_t aborted;
@@ -99,6 +100,7 @@ struct Params {
     int head_chunks;                       // dense mode: 64-column chunks between two kv heads of a cache row
     float scale_log2;
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
+    int q_tma, q_box_bytes;                // the first request's Q comes as 9 TMA boxes of q_box_bytes through the empty K ring
     __nv_bfloat16* out; int64_t o_sb, o_ss, o_sh;
     float* lse; int64_t l_sb, l_ss, l_sh;
     const int* block_table; int64_t bt_sb; const int* seqlens;
@@ -312,7 +314,8 @@ __device__ __forceinline__ const uint8_t* shfl_ptr(const uint8_t* ptr, int src_l
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
-attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const Params p) {
+attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const __grid_constant__ CUtensorMap qmap, const Params p) {
     using WalkerT = Walker<MODE>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -346,6 +349,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             mbar_init(smem_addr(&sm.corr_done[i]), 128);
         }
         mbar_init(smem_addr(&sm.q_ready), 256);
+        mbar_init(smem_addr(&sm.q_landed), 1);
+        mbar_init(smem_addr(&sm.ring_released), 256);
         mbar_init(smem_addr(&sm.fin_empty), 128);
         mbar_init(smem_addr(&sm.fin_full), 128);
         sm.aborted = 0;
@@ -354,6 +359,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             mbar_arrive_expect_tx(smem_addr(&sm.p_full[i]), P_SUB_BYTES + ((i & 1) == 0 ? 4 * SIDE_BYTES : 0));
         fence_mbar_init();
         if (MODE == MODE_DENSE) prefetch_tensormap(cta_rank == 0 ? &kmap : &vmap);
+        if (p.q_tma && cta_rank == 0) prefetch_tensormap(&qmap);
     }
     if (warp == 1) { tmem_alloc(smem_addr(&sm.tmem_base), 512); tmem_relinquish(); }
     tc_fence_before();
@@ -361,11 +367,32 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     tc_fence_after();
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
     if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
+#ifdef MLA_TRACE
+    if (threadIdx.x == 0 && cta_rank == 0 && part < 128 && row_blk == 0) { uint32_t smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_span[part][0][7] = smid; }
+#endif
     const uint32_t tmem = sm.tmem_base;
     // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
     // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
     Waiter wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
+    // A request's Q (score CTA): nine [rows][64 columns] boxes, chunks 0-6 into the K ring once the
+    // previous request's tiles have left it (the softmax warpgroups move them on to tensor memory and release the
+    // ring), chunks 7 and 8 into their final place.  Large boxes stream several times faster into one SM than
+    // per-thread loads, and the request boundary - where the MMA warp idles - is what this shortens.
+    auto issue_q = [&](const Work& w) {
+        const uint32_t bar = smem_addr(&sm.q_landed);
+        mbar_arrive_expect_tx(bar, 9u * (uint32_t)p.q_box_bytes);
+        // coordinates: (column, head, query token, request); prefill: a "request" is a query token of the only batch
+        const int c1 = MODE == MODE_SPARSE_DECODE ? 0 : MODE == MODE_PREFILL ? row_blk * ROWS : hk * p.g;
+        const int c2 = MODE == MODE_SPARSE_DECODE ? (int)blockIdx.y : MODE == MODE_PREFILL ? w.req : row_blk * (ROWS / p.g);
+        const int c3 = MODE == MODE_PREFILL ? 0 : w.req;
+#pragma unroll 1
+        for (int c = 0; c < 9; ++c) {
+            const uint32_t dst = c < Q_TMEM_CHUNKS ? smem_addr(sm.data + SC_KRING + c * 16384)
+                                                   : smem_addr(sm.data + SC_Q78 + (c - Q_TMEM_CHUNKS) * 16384);
+            tma_load_4d(dst, &qmap, bar, c * 64, c1, c2, c3);
+        }
+    };
 
     // =====================================================================================================
     // In the sparse modes the CTA has 512 threads that start with 128 registers each; every warpgroup re-sizes its
@@ -376,10 +403,24 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // ---------------- TMA producer (both CTAs) ---------------------------------------------------------
         if (MODE != MODE_DENSE) {
             // sparse modes: the gather warpgroup fills the rings
+            if (p.q_tma && cta_rank == 0 && lane == 0) {
+                uint32_t g = 0, nreq = 0;
+                for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
+                    const Work w = wk.get();
+                    issue_q(w);
+                    wt.wait<false>(&sm.ring_released, nreq & 1, 11);     // (a request without tiles must not be overtaken)
+                    // The next request's boxes may go out once every MMA of this one has finished with the ring and with
+                    // chunks 7, 8 of Q.  A parity wait only means what it says to a thread that has seen every earlier
+                    // phase of the barrier, so this thread follows the ring tile by tile.
+                    for (int i = 0; i < w.ntiles; ++i, ++g)
+                        for (int grp = 0; grp < 3; ++grp) wt.wait<false>(&sm.kv_empty[grp], g & 1, 13);
+                }
+            }
         } else if (lane == 0) {
             uint32_t ks = 0;                               // ring slot counter (K groups or V half-pages)
+            uint32_t nreq = 0;
             const int chunk0 = hk * p.head_chunks;         // the kv head's first 64-column chunk in the tensor maps
-            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
                 // page ids are fetched one tile ahead so the block-table latency stays off the TMA issue path
@@ -387,6 +428,13 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 if (w.ntiles > 0) {
                     nxt0 = __ldg(bt + w.blk_begin);
                     nxt1 = w.blk_begin + 1 < w.blk_end ? __ldg(bt + w.blk_begin + 1) : oob_page;
+                }
+                if (p.q_tma && cta_rank == 0) {
+                    // the K ring stages this request's Q first: wait until the previous request's tiles (and every MMA
+                    // that read its Q) are done, send the boxes, and take the ring back once they have been copied out
+                    for (int grp = 0; grp < 3; ++grp) wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 13);
+                    issue_q(w);
+                    wt.wait<false>(&sm.ring_released, nreq & 1, 11);
                 }
                 for (int i = 0; i < w.ntiles; ++i) {
                     const int page0 = nxt0, page1 = nxt1;
@@ -589,7 +637,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // for) into the 128-byte-swizzled operand layout; invalid tokens get zeros (zero-size source).  The ring
         // barrier counts one arrival per thread, made by the copy engine when that thread's copies have landed.
         const int gw = warp - 12;                                 // warp inside the gather warpgroup
-        uint32_t ks = 0, g = 0;
+        uint32_t ks = 0, g = 0, nreq_p = 0;
         uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
         if (MODE == MODE_SPARSE_DECODE) {
             // FP8 records: index -> (page, offset) -> 656-byte record = 512 e4m3 | 4 fp32 scales | 64 bf16 RoPE.
@@ -608,11 +656,15 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // are deliberately left rolled: with every instance unrolled the conversion code was several times the
             // instruction cache and the warps waited for instructions more than they computed.
             const int tq = blockIdx.y;
+            bool ring_lent = false;                                       // the K ring first stages every request's Q
+            uint32_t nreq_g = 0;
             float4 sc_cur = make_float4(0.f, 0.f, 0.f, 0.f);
             const uint32_t kring = smem_addr(sm.data + SC_KRING);
             const uint32_t vring = smem_addr(sm.data + VA_VRING);
-            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+            for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq_g) {
                 const Work w = wk.get();
+                ring_lent = p.q_tma && cta_rank == 0;
+                if (ring_lent && w.ntiles == 0) wt.wait<false>(&sm.ring_released, nreq_g & 1, 211);   // follow every phase
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
                 const int* idx1 = p.stopk[1] ? p.sidx[1] + (int64_t)w.req * p.sidx_sb[1] + (int64_t)tq * p.sidx_ss[1] : nullptr;
                 // index -> record address in two steps, so that the index of a tile can be loaded two tiles ahead and
@@ -652,6 +704,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         rec_next = rec_of(myblk + 2 * (i + 1), id_next);
                         sc_next = scales_of(rec_next);
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
+                        if (ring_lent) { wt.wait<false>(&sm.ring_released, nreq_g & 1, 211); ring_lent = false; }
 #pragma unroll 1
                         for (int grp = 0; grp < 3; ++grp, ++ks) {
                             GTRACE(0, ks);
@@ -713,8 +766,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
             }
         } else
-        for (WalkerT wk(p, part); wk.valid(); wk.next()) {
+        for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq_p) {
             const Work w = wk.get();
+            bool ring_lent = p.q_tma && cta_rank == 0;          // the K ring first stages this query token's Q
+            if (ring_lent && w.ntiles == 0) wt.wait<false>(&sm.ring_released, nreq_p & 1, 211);        // follow every phase
             const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
             // the index of a tile's token is loaded one tile ahead (a load that is used at once costs its latency)
             int id_next = -1;
@@ -739,6 +794,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const uint32_t ring0 = smem_addr(sm.data + SC_KRING) + gw * 32 * 128;
                     const int c = lane & 7;
                     GTRACE(0, ks);
+                    if (ring_lent) { wt.wait<false>(&sm.ring_released, nreq_p & 1, 211); ring_lent = false; }
                     wt.wait<false>(&sm.kv_empty[0], par, 201);
                     wt.wait<false>(&sm.kv_empty[1], par, 201);
                     GTRACE(1, ks);
@@ -824,9 +880,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // FP8 decode: these 256 threads also de-quantise the K tiles in place (two threads per token row, every other
             // 16-value piece each), one tile ahead of the softmax they compute: tile g + 1 is converted before the scores
             // of tile g are awaited, so the MMA warp has the next tile while this warpgroup is busy with the softmax.
-            uint32_t total_tiles = 0, conv_tile = 0;
-            if (MODE == MODE_SPARSE_DECODE)
-                for (WalkerT w2(p, part); w2.valid(); w2.next()) total_tiles += w2.get().ntiles;
+            uint32_t conv_tile = 0;
             Waiter wt_fast(p.status, &sm.aborted);                   // conversion sits on the MMA warp's critical path: no sleeping
             auto convert_tile = [&](const uint32_t tile) {
                 const int sw = r & 7;
@@ -868,6 +922,24 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         ? p.q + (int64_t)w.req * p.q_ss + (int64_t)hd * p.q_sh
                         : p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
                     const int c_begin = half ? 4 : 0, c_end = half ? 7 : 4, c_smem = half ? 8 : 7;
+                    if (p.q_tma) {
+                        // Q arrived as TMA boxes: chunks 7 and 8 are in place, chunks 0-6 wait in the K ring as
+                        // [row][128 B] with the 128-byte swizzle
+                        wt.wait<false>(&sm.q_landed, nreq & 1, 12);
+#pragma unroll 1
+                        for (int c = c_begin; c < c_end; ++c) {
+                            const uint8_t* qsrc = sm.data + SC_KRING + c * 16384 + r * 128;
+                            uint32_t v[32];
+#pragma unroll
+                            for (int ch = 0; ch < 8; ++ch) {
+                                const uint4 x = *reinterpret_cast<const uint4*>(qsrc + ((ch ^ (r & 7)) << 4));
+                                v[4 * ch] = x.x; v[4 * ch + 1] = x.y; v[4 * ch + 2] = x.z; v[4 * ch + 3] = x.w;
+                            }
+                            tmem_st32(tlane + TM_Q + c * 32, v);
+                        }
+                        tmem_wait_st();
+                        mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
+                    } else
 #pragma unroll 1
                     for (int c = c_begin; c <= c_end; ++c) {
                         const int chunk = c < c_end ? c : c_smem;
@@ -903,7 +975,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t sb = g & 1, ph = (g >> 1) & 1;
                     if (MODE == MODE_SPARSE_DECODE)
-                        while (conv_tile <= g + 1 && conv_tile < total_tiles) convert_tile(conv_tile++);
+                        // one tile ahead, but never into the next request: its first tile can only be gathered after
+                        // these threads have moved that request's Q out of the K ring
+                        while (conv_tile <= g + 1 && conv_tile < g + (uint32_t)(w.ntiles - i)) convert_tile(conv_tile++);
                     wt.wait<false>(&sm.s_full[sb], ph, 5);
                     tc_fence_after();
                     if (threadIdx.x == 128) TRACE(3, g);
@@ -1251,6 +1325,33 @@ bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
     return true;
 }
 
+// Tensor map over Q as (576 columns, heads, query tokens, requests) with boxes of 64 columns x box_h heads x box_t
+// tokens, for the first request of every partition.  Returns false (the kernels then load every Q with their own
+// threads) when Q's base or strides do not meet TMA's 16-byte rules or the driver rejects the map.
+static bool encode_q_map(CUtensorMap* qmap, const void* q, int b, int s_q, int h_q, int64_t sb, int64_t ss, int64_t sh,
+                         int box_h, int box_t, int* box_bytes) {
+    using namespace sm100;
+    static const bool enabled = [] { const char* e = getenv("MLA_Q_TMA"); return !(e && e[0] == '0'); }();
+    EncodeTiledFn encode = get_encode_fn();
+    if (!enabled || !encode || !q) return false;
+    if (h_q <= 1) sh = 576;                         // a dimension of extent 1 never strides: give it a legal value
+    if (s_q <= 1) ss = sh * h_q;
+    if (b <= 1) sb = ss * s_q;
+    if ((reinterpret_cast<uintptr_t>(q) & 15) || sb <= 0 || ss <= 0 || sh <= 0 || (sb % 8) || (ss % 8) || (sh % 8)) return false;
+    if (sb * 2 >= (1ll << 40) || ss * 2 >= (1ll << 40) || sh * 2 >= (1ll << 40)) return false;
+    if (box_h < 1 || box_h > 256 || box_t < 1 || box_t > 256 || box_h * box_t > ROWS) return false;
+    cuuint64_t dims[4] = {576, (cuuint64_t)h_q, (cuuint64_t)s_q, (cuuint64_t)b};
+    cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_h, (cuuint32_t)box_t, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = encode(qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return false;
+    *box_bytes = 128 * box_h * box_t;
+    return true;
+}
+
 int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     using namespace sm100;
     EncodeTiledFn encode = get_encode_fn();
@@ -1291,6 +1392,11 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
     p.num_blocks = a.num_blocks;
     p.head_chunks = head_chunks;
+    CUtensorMap qmap;
+    memset(&qmap, 0, sizeof(qmap));
+    if (p.row_blocks == 1 || ROWS % p.g == 0)
+        p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h, p.g,
+                               p.row_blocks == 1 ? a.s_q : ROWS / p.g, &p.q_box_bytes) ? 1 : 0;
 
     static bool configured[64] = {};
     int dev = 0;
@@ -1300,7 +1406,7 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
         if (dev < 64) configured[dev] = true;
     }
     dim3 grid(2, p.row_blocks * a.h_kv, a.num_sm_parts);
-    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, vmap, p);
+    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, vmap, qmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1342,7 +1448,11 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     if (pairs < 1) pairs = 1;
     if (pairs > a.s_q) pairs = a.s_q;
     dim3 grid(2, p.row_blocks, pairs);
-    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, p);
+    CUtensorMap qmap;
+    memset(&qmap, 0, sizeof(qmap));
+    p.q_tma = encode_q_map(&qmap, a.q, 1, a.s_q, a.h_q, 0, a.q_stride_s, a.q_stride_h, a.h_q < ROWS ? a.h_q : ROWS, 1,
+                           &p.q_box_bytes) ? 1 : 0;
+    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, qmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1382,10 +1492,13 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
         MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_SPARSE_DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
         if (dev < 64) configured[dev] = true;
     }
-    CUtensorMap unused_map;
-    memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers with its own threads, no TMA descriptor
+    CUtensorMap unused_map, qmap;
+    memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers K and V with its own threads
+    memset(&qmap, 0, sizeof(qmap));
+    p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h,
+                           a.h_q < ROWS ? a.h_q : ROWS, 1, &p.q_box_bytes) ? 1 : 0;
     dim3 grid(2, a.s_q, a.num_sm_parts);
-    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, p);
+    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, qmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

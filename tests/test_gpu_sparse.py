@@ -195,3 +195,37 @@ def test_fp8_cache_writer_bit_exact(golden_dir):
     got = quantize_fp8_kvcache(c["x"].to(DEV), pow2_scale=True, pad_rows=1)
     assert got.stride(0) == c["quant_stride0"]
     assert torch.equal(got.view(torch.uint8).contiguous().cpu().reshape(-1), c["quant_bytes"].reshape(-1))
+
+
+@pytest.mark.parametrize("ragged", [False, True])
+def test_sparse_decode_many_requests_per_partition(ragged):
+    """More requests than SM partitions: every CTA pair walks several requests (and, with per-request lengths,
+    partitions that split requests), so the hand-over of Q, of the K ring and of the accumulators between
+    requests is what this checks; two runs must agree bit for bit."""
+    from flashmla_b200 import workloads as W
+    b, h_q, s_kv, topk = 190, 128, 1024, 256
+    d = W.sparse_decode_inputs(b, 1, h_q, s_kv, topk, seed=11, device="cpu")
+    kv_deq = quant.dequantize_v32(d["kv_fp8"])
+    topk_length = torch.randint(0, topk + 1, (b,), generator=torch.Generator().manual_seed(5), dtype=torch.int32) if ragged else None
+    ref_out, ref_lse = attention.sparse_decode(d["q"], kv_deq, d["indices"], 576 ** -0.5, 512, None, topk_length)
+    args = (d["q"].to(DEV), d["kv_fp8"].to(DEV), d["indices"].to(DEV), 576 ** -0.5, None, _dev(topk_length))
+    out, lse = _decode(*args)
+    out2, lse2 = _decode(*args)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+
+
+def test_sparse_prefill_many_query_tokens_per_cta_pair():
+    """More query tokens than CTA pairs: every pair strides over several tokens, each with its own Q hand-over
+    through the K ring; two runs must agree bit for bit."""
+    from flashmla_b200 import workloads as W
+    d = W.sparse_prefill_inputs(333, 128, 2048, 384, seed=9, device="cpu")
+    ref = attention.sparse_prefill(d["q"], d["kv"], d["indices"], 576 ** -0.5, 512)
+    args = (d["q"].to(DEV), d["kv"].to(DEV), d["indices"].to(DEV), 576 ** -0.5)
+    out, mx, lse = _prefill(*args)
+    out2, mx2, lse2 = _prefill(*args)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2) and torch.equal(mx, mx2)
+    assert_out_close("out", out, ref[0])
+    assert_lse_close("max_logits", mx, ref[1])
+    assert_lse_close("lse", lse, ref[2])
