@@ -207,7 +207,15 @@ struct Walker<MODE_PREFILL> {
     __device__ void next() { req += gridDim.z; }
 };
 
-// Bounded wait helper: after the first expiry the thread stops waiting altogether.
+#ifndef MLA_PRESPIN_DENSE
+#define MLA_PRESPIN_DENSE 0
+#endif
+#ifndef MLA_PRESPIN_GATHER
+#define MLA_PRESPIN_GATHER 64
+#endif
+// Bounded wait helper: after the first expiry the thread stops waiting altogether.  LEAN: no unrolled probes before
+// the timed loop (dense mode).
+template <bool LEAN>
 struct Waiter {
     bool aborted = false;
     bool parked;                         // park the thread between probes instead of spinning
@@ -219,7 +227,7 @@ struct Waiter {
     __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
         if (aborted) return;
         const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT, sleep_ns)
-                               : mbar_wait_bounded<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT);
+                               : mbar_wait_bounded<CLUSTER, LEAN ? MLA_PRESPIN_DENSE : MLA_PRESPIN_GATHER>(smem_addr(bar), parity, WAIT_LIMIT);
         if (!ok) {
             aborted = true;
             *smem_flag = 1;
@@ -373,7 +381,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     const uint32_t tmem = sm.tmem_base;
     // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
     // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
-    Waiter wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
+    using WaiterT = Waiter<MODE == MODE_DENSE>;
+    WaiterT wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
     // A request's Q (score CTA): nine [rows][64 columns] boxes, chunks 0-6 into the K ring once the
     // previous request's tiles have left it (the softmax warpgroups move them on to tensor memory and release the
@@ -881,7 +890,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             // 16-value piece each), one tile ahead of the softmax they compute: tile g + 1 is converted before the scores
             // of tile g are awaited, so the MMA warp has the next tile while this warpgroup is busy with the softmax.
             uint32_t conv_tile = 0;
-            Waiter wt_fast(p.status, &sm.aborted);                   // conversion sits on the MMA warp's critical path: no sleeping
+            WaiterT wt_fast(p.status, &sm.aborted);                   // conversion sits on the MMA warp's critical path: no sleeping
             auto convert_tile = [&](const uint32_t tile) {
                 const int sw = r & 7;
                 float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -1209,7 +1218,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const int trow = r & 63, hb = r >> 6, sw = trow & 7;
             const int tq = blockIdx.y;
             uint32_t ks = 0;
-            Waiter wt_fast(p.status, &sm.aborted);               // this sits on the MMA warp's critical path: no sleeping
+            WaiterT wt_fast(p.status, &sm.aborted);               // this sits on the MMA warp's critical path: no sleeping
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
