@@ -506,7 +506,7 @@ def main():
     # DRAM traffic per launch from the ncu capture summarised under profiles/ (dram__bytes_read + write): only the
     # default dense workload has been captured; traffic scales with the workload's bytes, so it is given per launch
     # of exactly that workload and left null otherwise.
-    roof["traffic"] = 676.2e6 if (args.workload == "dense" and world == 1) else None
+    roof["traffic"] = 681.9e6 if (args.workload == "dense" and world == 1) else None
     roof["kernel"] = main_kernel
     roof["kernel_ms"] = k_ms
     roof["peak_source"] = peaks["source"]
