@@ -59,6 +59,9 @@ def test_config1_tiny():
 @pytest.mark.parametrize("s_q,h_q,h_kv,causal", [
     (1, 128, 1, False), (2, 128, 1, True), (1, 64, 1, False), (4, 9, 1, True), (2, 126, 2, True), (1, 3, 3, False),
     (2, 63, 1, True), (1, 1, 1, False),
+    # two row blocks: Q boxes of 2 tokens x 64 heads per block / a group size that does not divide a row block
+    # (Q is then loaded by the kernel's own threads)
+    (4, 64, 1, True), (4, 48, 1, True),
 ])
 def test_shape_grid(s_q, h_q, h_kv, causal):
     seqlens = [140, 4096 // 8 + 3, 20, 0, 64, 1, 1000, 65]
