@@ -389,6 +389,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     // ring), chunks 7 and 8 into their final place.  Large boxes stream several times faster into one SM than
     // per-thread loads, and the request boundary - where the MMA warp idles - is what this shortens.
     auto issue_q = [&](const Work& w) {
+        if (wt.aborted) return;                    // never arm a barrier whose previous phase may still be open
         const uint32_t bar = smem_addr(&sm.q_landed);
         mbar_arrive_expect_tx(bar, 9u * (uint32_t)p.q_box_bytes);
         // coordinates: (column, head, query token, request); prefill: a "request" is a query token of the only batch
@@ -455,6 +456,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     if (cta_rank == 0) {
                         for (int grp = 0; grp < 3; ++grp, ++ks) {
                             wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 1);
+                            if (wt.aborted) continue;      // never arm a barrier whose previous phase may still be open
                             if (grp == 0) TRACE(0, ks / 3);
                             if (grp == 2) TRACE(7, ks / 3);
                             const uint32_t bar = smem_addr(&sm.kv_full[grp]);
@@ -470,6 +472,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
                                 wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
+                                if (wt.aborted) continue;  // never arm a barrier whose previous phase may still be open
                                 const uint32_t bar = smem_addr(&sm.kv_full[slot]);
                                 mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
                                 const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
