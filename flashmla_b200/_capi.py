@@ -6,7 +6,7 @@ or unloadable library raises.
 import ctypes
 import os
 import threading
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_longlong, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FLASHMLA_B200_LIB") or os.path.join(_HERE, "libflashmla_b200.so")
@@ -15,7 +15,9 @@ MLA_MODE_DENSE_DECODE = 0
 MLA_MODE_SPARSE_DECODE = 1
 
 IMPL_AUTO, IMPL_PORTABLE, IMPL_TCGEN05 = 0, 1, 2
-NOALLOC_MAX_ROWS = 16384
+NOALLOC_MAX_ROWS = 32768
+MLA_DTYPE_BF16, MLA_DTYPE_FP16 = 0, 1
+ABI_VERSION = 2
 
 
 class SchedMetaArgs(Structure):
@@ -40,7 +42,7 @@ class DenseDecodeArgs(Structure):
         ("lse", c_void_p), ("lse_stride_b", c_int64), ("lse_stride_s", c_int64), ("lse_stride_h", c_int64),
         ("meta", c_void_p), ("num_splits", c_void_p), ("num_sm_parts", c_int32),
         ("lse_accum", c_void_p), ("o_accum", c_void_p),
-        ("status", c_void_p), ("impl", c_int32), ("stream", c_void_p),
+        ("status", c_void_p), ("impl", c_int32), ("dtype", c_int32), ("stream", c_void_p),
     ]
 
 
@@ -70,7 +72,7 @@ class CombineArgs(Structure):
         ("lse", c_void_p), ("lse_stride_b", c_int64), ("lse_stride_s", c_int64), ("lse_stride_h", c_int64),
         ("out", c_void_p), ("o_stride_b", c_int64), ("o_stride_s", c_int64), ("o_stride_h", c_int64),
         ("lse_accum", c_void_p), ("o_accum", c_void_p), ("num_splits", c_void_p), ("attn_sink", c_void_p),
-        ("stream", c_void_p),
+        ("dtype", c_int32), ("_pad", c_int32), ("stream", c_void_p),
     ]
 
 
@@ -109,6 +111,8 @@ SYMBOLS = {
     "mla_sparse_prefill_fwd": (c_int, [POINTER(SparsePrefillArgs)]),
     "mla_dense_decode_noalloc": (c_int, [POINTER(DenseDecodeArgs)]),
     "mla_quantize_fp8_kvcache": (c_int, [POINTER(QuantizeArgs)]),
+    "mla_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, POINTER(c_size_t)]),
+    "mla_selftest_bounded_wait": (c_int, [c_longlong, c_int, c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None
@@ -130,6 +134,9 @@ def lib():
                     fn = getattr(handle, name)
                     fn.restype = restype
                     fn.argtypes = argtypes
+                if handle.mla_abi_version() != ABI_VERSION:
+                    raise RuntimeError(f"{LIB_PATH} has ABI version {handle.mla_abi_version()}, this package needs "
+                                       f"{ABI_VERSION}: rebuild it with `python -m flashmla_b200.build --force`")
                 _lib = handle
     return _lib
 

@@ -48,6 +48,7 @@ struct Params {
     // dense
     const __nv_bfloat16* kc; int64_t k_sblock, k_srow, k_shead;
     const int* block_table; int64_t bt_sb; const int* seqlens; int causal;
+    int max_blocks;               // width of the block table: blocks at or beyond it read no table entry and count as invalid
     // sparse fp8 (two scopes: main, extra)
     const uint8_t* kvb[2]; int64_t kvb_sblock[2]; int pbs[2]; int nblocks[2];
     const int* idx[2]; int64_t idx_sb[2], idx_ss[2]; int topk[2]; const int* topk_len[2];
@@ -127,7 +128,7 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
     __nv_bfloat16* dst = sm.k[buf];
     if (MODE == DENSE) {
         const int blk = st >> 1;
-        const int page = p.block_table[s.req * p.bt_sb + blk];
+        const int page = blk < p.max_blocks ? p.block_table[(int64_t)s.req * p.bt_sb + blk] : -1;
         const bool page_ok = page >= 0 && page < p.nblocks[0];
         const __nv_bfloat16* base = p.kc + (int64_t)page * p.k_sblock + (int64_t)s.hk * p.k_shead;
         for (int c = tid; c < BN * 72; c += NTHREADS) {
@@ -473,6 +474,7 @@ int launch_dense_decode_portable(const mla_dense_decode_args_t& a) {
     p.lse = a.lse; p.l_sb = a.lse_stride_b; p.l_ss = a.lse_stride_s; p.l_sh = a.lse_stride_h;
     p.kc = (const __nv_bfloat16*)a.k_cache; p.k_sblock = a.k_stride_block; p.k_srow = a.k_stride_row; p.k_shead = a.k_stride_head;
     p.block_table = a.block_table; p.bt_sb = a.block_table_stride_b; p.seqlens = a.seqlens_k; p.nblocks[0] = a.num_blocks;
+    p.max_blocks = a.max_blocks_per_seq;
     p.causal = a.is_causal && a.s_q > 1;
     p.meta = a.meta; p.num_splits = a.num_splits; p.lse_accum = a.lse_accum; p.o_accum = a.o_accum;
     dim3 grid((p.rows + portable::BM - 1) / portable::BM, a.h_kv, a.num_sm_parts);

@@ -1,41 +1,58 @@
-// Dense BF16 paged MLA decode for sm_100a: tcgen05 MMAs with TMEM accumulators, fed by TMA loads of
-// 64-token KV pages through the block table.
+// MLA attention for sm_100a: tcgen05 MMAs with TMEM accumulators.  One kernel template serves
+//   MODE_DENSE          dense BF16 / FP16 paged decode, fed by TMA loads of 64-token KV pages through the block table
+//   MODE_PREFILL        token-sparse prefill, KV rows gathered by index with cp.async
+//   MODE_SPARSE_DECODE  sparse FP8 decode, 656-byte records gathered by index and de-quantised in shared memory
 //
 // Problem shape per (request, kv head): 128 query rows (query token x head, padded with zero rows)
-// against a paged stream of 576-wide K rows whose first 512 columns are also V.  The fp32 output
+// against a stream of 576-wide K rows whose first 512 columns are also V.  The fp32 output
 // accumulator O[128 x 512] fills all 512 columns of one SM's tensor memory, so the work of one row
 // block is split over a CLUSTER OF TWO CTAs on two SMs that walk the same KV range in tiles of 128
 // tokens (two pages):
 //
 //   CTA 0 ("score" CTA)  S = Q K^T: 36 MMAs 128x128x16 per tile (N = 128 runs the tensor pipe at full
-//       rate, N = 64 does not).  Q is the A operand: dims 0..447 live in tensor memory (224 columns of
-//       packed bf16), dims 448..575 in shared memory; two S accumulators (2 x 128 columns).  K arrives
-//       through a TMA ring of three 48 KB groups; a group is three 64-dim chunks of a tile (each
-//       [128 tokens][64 dims], K-major, 128-byte swizzle) and is refilled as soon as its twelve MMAs
-//       have retired.
+//       rate, N = 64 does not).  Q is the A operand and lives in tensor memory (packed bf16).  K arrives
+//       through a ring of 48 KB groups; a group is three 64-dim chunks of a tile (each [128 tokens][64 dims],
+//       K-major, 128-byte swizzle) and is refilled as soon as its twelve MMAs have retired.
+//         dense mode:   all 576 dims of Q in tensor memory (288 columns) next to ONE S accumulator (128 columns);
+//                       the shared memory this frees makes the ring FOUR groups deep (192 KB): the time a tile
+//                       takes is the refill latency of a ring slot divided by the slots that can be in flight.
+//         gather modes: dims 0..447 of Q in tensor memory, dims 448..575 in shared memory, two S accumulators,
+//                       a ring of three groups.
 //       Two softmax warpgroups (one per page of the tile, one thread per row and page) exchange row
 //       maxima through shared memory, write P (bf16) in MMA operand layout to a staging buffer and
 //       push it to CTA 1 with bulk shared-to-shared copies that complete on CTA 1's barriers.
 //   CTA 1 ("value" CTA)  O += P V: per page 2 x 4 MMAs 128x256x16 (A = P from shared memory, B = the
-//       first 512 dims of the page viewed MN-major; 5-slot TMA ring of [64 tokens][256 dims]),
+//       first 512 dims of the page viewed MN-major; 5-slot ring of [64 tokens][256 dims]),
 //       the rare O rescale, and the epilogue (normalise; bf16 output or fp32 split partials).
 //
 // The tensor work divides 576 : 512 between the two SMs; each KV page is fetched from HBM by whichever
-// CTA asks first and from L2 by the other.  No TMA multicast is used.
+// CTA asks first and from L2 by the other.  No TMA multicast is used.  (MMAs that span the CTA pair,
+// cta_group::2, were considered and not used: with 64 of the 128 rows per CTA each CTA still has to stage its
+// half of the tokens for Q K^T and ALL tokens of its half of the columns for P V - 136 KB per tile and CTA
+// against 144 + 128 KB here - so neither the bytes that enter the SMs nor the ring depth improve.)
 //
 // Softmax uses the running maximum lazily: O is rescaled only when a row's maximum grew by more than 2^6
 // since the value in use; P, the row sum and O always refer to the same maximum, so results are exact
 // up to rounding.
 //
-// Every mbarrier wait is bounded (about a second); on expiry the thread records a code in the status
-// words, stops waiting and the CTA pair winds down normally (tensor memory is released, both CTAs
-// leave together).
+// Every mbarrier wait is bounded (Params::wait_limit SM cycles, about a second by default).  A thread whose
+// wait ran out records a code in the status words, raises the `aborted` flag of both CTAs and LEAVES its role:
+// it issues no further arrival, MMA or copy.  Single-thread roles leave at once; warps leave together (a vote
+// after every wait, because tcgen05.ld/st are warp-collective); the two softmax warpgroups, which meet at a
+// named barrier every tile, carry the flag through that barrier (bar.red.or) and leave together behind it.
+// Threads that depend on the one that left run into their own limit.  The wind-down then waits - again
+// bounded - for this CTA's own MMAs and TMA loads, meets the peer CTA, gives copies between the two CTAs time
+// to land, and only then frees tensor memory; both CTAs leave together.
 //
 // Behavioural reference: csrc/sm90/decode/dense/splitkv_mla.cuh:959-1272 (masking, split / direct
-// epilogue, empty rows) of deepseek-ai/FlashMLA; the reference has no sm_100 dense decode kernel.
+// epilogue, empty rows), csrc/sm100/decode/head64/kernel.cuh:19-849 (FP8 records, validity, attn_sink) and
+// csrc/sm100/prefill/sparse/fwd/head128/phase1.cuh:65-614 (prefill outputs) of deepseek-ai/FlashMLA.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include <cuda_fp16.h>
 #include <string.h>
+#include <stdlib.h>
+#include <mutex>
 
 namespace mla {
 namespace sm100 {
@@ -44,63 +61,81 @@ using namespace ptx;
 
 constexpr int ROWS = 128;
 constexpr int PAGE = 64;              // tokens per page
-constexpr int D_QK = 576, D_V = 512;
-constexpr int BOX_BYTES = 8192;       // one TMA box: 64 tokens x 64 bf16, 128-byte swizzled rows
+constexpr int D_V = 512;             // value columns = the first 512 of the 576 key columns
+constexpr int BOX_BYTES = 8192;       // 64 tokens x 64 bf16, 128-byte swizzled rows
 constexpr int K_CHUNK_BYTES = 2 * BOX_BYTES;  // one 64-dim chunk of a tile: [128 tokens][64 dims]
 constexpr int K_GROUP_BYTES = 3 * K_CHUNK_BYTES;   // the K ring moves in groups of 3 chunks (one barrier pair per group)
-constexpr int NKS = 3;                        // K ring slots = groups per tile: group j of every tile uses slot j
 constexpr int V_SLOT_BYTES = 4 * BOX_BYTES;   // half a page of V: [64 tokens][256 dims] as 4 boxes
 constexpr int NVS = 5;                        // V ring slots
 constexpr int P_SUB_BYTES = ROWS * PAGE * 2;  // P of one page: [128 rows][64 tokens] bf16
 constexpr int NPB = 4;                        // P buffers in the value CTA: (tile parity, page of the tile)
-constexpr int NRING = NKS > NVS ? NKS : NVS;
+constexpr int NRING = 5;                      // ring barriers: K groups (score CTA, 3 or 4) / V slots (value CTA, 5)
 constexpr int SIDE_BYTES = 144;               // per warp and tile: 32 rescale factors + flag (+ pad)
 constexpr int NTHREADS = 384;                 // dense mode: control warpgroup + two softmax / correction warpgroups
 constexpr int NTHREADS_GATHER = 512;          // sparse modes: one more warpgroup that gathers KV rows by index
-constexpr long long WAIT_LIMIT = 2000000000LL;    // SM cycles (about one second)
+constexpr long long WAIT_LIMIT_DEFAULT = 2000000000LL;    // SM cycles (about one second)
+constexpr long long DRAIN_LIMIT = 4000000LL;              // wind-down after an expired wait: per tracked operation
+constexpr long long SETTLE_CYCLES = 400000LL;             // ... and for copies between the two CTAs
 #ifndef MLA_SLEEP_NS
 #define MLA_SLEEP_NS 200u
 #endif
 constexpr float RESCALE_THRESHOLD = 6.0f;         // log2 units
 
-// tensor-memory columns of the score CTA: two S accumulators and the first 7 chunks of Q
-constexpr uint32_t TM_S = 0, TM_Q = 256;
-constexpr int Q_TMEM_CHUNKS = 7;
+enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
 
-// byte offsets inside Smem::data
-constexpr int SC_Q78 = 0;                                   // score CTA: Q dims 448..575, 2 x [128][64]
-constexpr int SC_KRING = SC_Q78 + 2 * 16384;
-constexpr int SC_STAGE = SC_KRING + NKS * K_GROUP_BYTES;     // 8 warps x 4 KB P staging
-constexpr int SC_SIDE = SC_STAGE + 8 * 4096;                // 4 warps x 144 B factor/flag staging
-constexpr int SC_XMAX = SC_SIDE + 4 * SIDE_BYTES;           // [2][2][128] floats
-constexpr int SC_END = SC_XMAX + 2 * 2 * ROWS * 4;
-constexpr int VA_VRING = 0;                                 // value CTA
+// Shared-memory and tensor-memory plan of the score CTA, per mode (byte offsets inside Smem::data).
+template <int MODE>
+struct Lay {
+    static constexpr bool DENSE = MODE == MODE_DENSE;
+    static constexpr int NKS = DENSE ? 4 : 3;             // K ring slots; group j of tile g uses slot (3 g + j) mod NKS
+    static constexpr int S_BUFS = DENSE ? 1 : 2;          // S accumulators in tensor memory
+    static constexpr int Q_TMEM_CHUNKS = DENSE ? 9 : 7;   // 64-dim chunks of Q kept in tensor memory (the rest in SC_Q78)
+    static constexpr int Q_SPLIT = DENSE ? 5 : 4;         // chunks [0, Q_SPLIT) are moved there by softmax warpgroup 0, the others by 1
+    static constexpr uint32_t TM_S = 0, TM_Q = 128 * S_BUFS;
+    static constexpr int SC_Q78 = 0;                                    // gather modes: Q dims 448..575, 2 x [128][64]
+    static constexpr int SC_KRING = DENSE ? 0 : 2 * 16384;
+    static constexpr int SC_STAGE = SC_KRING + NKS * K_GROUP_BYTES;     // 8 warps x 4 KB P staging
+    static constexpr int SC_SIDE = SC_STAGE + 8 * 4096;                 // 4 warps x 144 B factor/flag staging
+    static constexpr int SC_XMAX = SC_SIDE + 4 * SIDE_BYTES;            // [2][2][128] floats
+    static constexpr int SC_END = SC_XMAX + 2 * 2 * ROWS * 4;
+    // gather modes only
+    static constexpr int SC_MASK = SC_END;                // validity bits of the last 4 tiles, [4][4] words
+    static constexpr int SC_LSUM = SC_MASK + 64;          // row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
+    static constexpr int SC_SCALES = SC_LSUM + ROWS * 4;  // FP8 decode: the 4 scales of every token of the last two tiles, [2][128] float4
+    static constexpr int SC_TOTAL = DENSE ? SC_END : SC_SCALES + 2 * ROWS * 16;
+    static_assert(TM_Q + Q_TMEM_CHUNKS * 32 <= 512, "tensor-memory columns of the score CTA");
+};
+// value CTA (all modes)
+constexpr int VA_VRING = 0;
 constexpr int VA_P = VA_VRING + NVS * V_SLOT_BYTES;
-constexpr int VA_END = VA_P + NPB * P_SUB_BYTES;
-constexpr int DATA_BYTES = VA_END > SC_END ? VA_END : SC_END;
+constexpr int VA_SIDE = VA_P + NPB * P_SUB_BYTES;         // factors + flag received with the first page of tile parity 0 / 1: [2][4][SIDE_BYTES]
+constexpr int VA_FIN = VA_SIDE + 2 * 4 * SIDE_BYTES;      // final row sum / running maximum / true maximum of the request: 3 x [128] floats
+constexpr int VA_END = VA_FIN + 3 * ROWS * 4;
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
+constexpr int DATA_BYTES = cmax(cmax(VA_END, Lay<MODE_DENSE>::SC_TOTAL), cmax(Lay<MODE_PREFILL>::SC_TOTAL, Lay<MODE_SPARSE_DECODE>::SC_TOTAL));
 
 struct Smem {
     uint8_t data[DATA_BYTES];
-    uint8_t side[2][4][SIDE_BYTES];      // value CTA: factors + flag received with the first page of tile parity 0 / 1
-    float fin_l[ROWS], fin_m[ROWS];      // value CTA: final row sum / running maximum of the request
-    float fin_mt[ROWS];                  // value CTA: true row maximum (the running maximum may lag it by up to 2^6)
     uint64_t kv_full[NRING], kv_empty[NRING];     // K groups (score CTA) / V slots (value CTA)
     uint64_t s_full[2], s_empty[2], q_ready, stage_full[2];
     uint64_t p_empty[NPB], stage_free[2], fin_empty;              // live in the score CTA, arrived by the value CTA
     uint64_t p_full[NPB], pv_done[NPB], corr_done[NPB], fin_full; // live in the value CTA
-    uint64_t q_landed, ring_released;    // score CTA: the first request's Q boxes have landed / have been copied out of the K ring
+    uint64_t q_landed, ring_released;    // score CTA: a request's Q boxes have landed / have been copied out of the K ring
     uint64_t raw_full[NRING];            // FP8 decode: the raw records of a K group (score CTA) / V slot (value CTA) have landed
+    uint64_t drain;                      // wind-down after an expired wait: this CTA's MMAs have retired
     uint32_t tmem_base;
-    uint32_t aborted;
+    uint32_t aborted;                    // a bounded wait ran out in this CTA or in its peer
 };
 static_assert(sizeof(Smem) <= 232448, "shared memory budget");
 
 struct Params {
     int b, s_q, h_q, h_kv, g, rows, causal, num_blocks;
     int head_chunks;                       // dense mode: 64-column chunks between two kv heads of a cache row
+    int max_blocks;                        // dense mode: width of the block table
     float scale_log2;
+    long long wait_limit;                  // SM cycles after which a barrier wait gives up
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
-    int q_tma, q_box_bytes;                // the first request's Q comes as 9 TMA boxes of q_box_bytes through the empty K ring
+    int q_tma, q_box_bytes;                // a request's Q comes as 9 TMA boxes of q_box_bytes through the empty K ring
     __nv_bfloat16* out; int64_t o_sb, o_ss, o_sh;
     float* lse; int64_t l_sb, l_ss, l_sh;
     const int* block_table; int64_t bt_sb; const int* seqlens;
@@ -116,12 +151,6 @@ struct Params {
     const int* sidx[2]; int64_t sidx_sb[2], sidx_ss[2]; int stopk[2]; const int* stopk_len[2];
     const float* attn_sink; float* max_logits;
 };
-
-enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
-constexpr int SC_MASK = SC_END;          // score CTA, prefill: validity bits of the last 4 tiles, [4][4] words
-constexpr int SC_LSUM = SC_MASK + 64;    // score CTA: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
-constexpr int SC_SCALES = SC_LSUM + ROWS * 4;   // score CTA, FP8 decode: the 4 scales of every token of the last two tiles, [2][128] float4
-static_assert(SC_SCALES + 2 * ROWS * 16 <= DATA_BYTES, "score CTA scratch must fit");
 
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
@@ -213,70 +242,61 @@ struct Walker<MODE_PREFILL> {
 #ifndef MLA_PRESPIN_GATHER
 #define MLA_PRESPIN_GATHER 64
 #endif
-// Bounded wait helper: after the first expiry the thread stops waiting altogether.  LEAN: no unrolled probes before
-// the timed loop (dense mode).
+
+// What a thread does when one of its bounded waits runs out: first code and a count in the global status words,
+// the `aborted` flag of this CTA and of its peer.  Shared with the self-test kernel at the end of this file.
+__device__ __forceinline__ void report_expired_wait(int* status, uint32_t* flag, uint32_t peer_flag, int code) {
+    *reinterpret_cast<volatile uint32_t*>(flag) = 1;
+    if (peer_flag) st_cluster_u32(peer_flag, 1u);
+    if (status) { atomicCAS(status, 0, code); atomicAdd(status + 1, 1); }
+}
+
+// Bounded wait helper.  wait() returns false when the wait ran out now or earlier: the caller leaves its role.
+// LEAN: no unrolled probes before the timed loop (dense mode).
 template <bool LEAN>
 struct Waiter {
     bool aborted = false;
     bool parked;                         // park the thread between probes instead of spinning
     uint32_t sleep_ns;                   // ... and sleep this long between probes
+    long long limit;
     int* status;
-    uint32_t* smem_flag;
-    __device__ Waiter(int* st, uint32_t* flag, bool park = false, uint32_t sleep = 0) : parked(park), sleep_ns(sleep), status(st), smem_flag(flag) {}
+    uint32_t* flag;
+    uint32_t peer_flag;
+    __device__ Waiter(int* st, uint32_t* flag_, uint32_t peer_flag_, long long limit_, bool park = false, uint32_t sleep = 0)
+        : parked(park), sleep_ns(sleep), limit(limit_), status(st), flag(flag_), peer_flag(peer_flag_) {}
     template <bool CLUSTER>
-    __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int code) {
-        if (aborted) return;
-        const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, WAIT_LIMIT, sleep_ns)
-                               : mbar_wait_bounded<CLUSTER, LEAN ? MLA_PRESPIN_DENSE : MLA_PRESPIN_GATHER>(smem_addr(bar), parity, WAIT_LIMIT);
+    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, int code) {
+        if (aborted) return false;
+        const bool ok = parked ? mbar_wait_bounded_parked<CLUSTER>(smem_addr(bar), parity, limit, sleep_ns)
+                               : mbar_wait_bounded<CLUSTER, LEAN ? MLA_PRESPIN_DENSE : MLA_PRESPIN_GATHER>(smem_addr(bar), parity, limit);
         if (!ok) {
             aborted = true;
-            *smem_flag = 1;
-            if (status) { atomicCAS(status, 0, code); atomicAdd(status + 1, 1); }
+            report_expired_wait(status, flag, peer_flag, code);
         }
+        return ok;
     }
 };
 
-#ifdef MLA_TRACE
-// Debug builds only: per-tile timestamps of every pipeline role of partition 0.
-__device__ unsigned long long g_trace[16][512];
-__device__ __forceinline__ void trace_ev(int part, int row_blk, int ev, uint32_t g) {
-    if (part == 0 && row_blk == 0 && g < 512) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_trace[ev][g] = t;
-    }
-}
-// Coarse per-partition timeline: [partition][event][occurrence]
-__device__ unsigned long long g_span[128][8][8];
-__device__ __forceinline__ void span_ev(int part, int row_blk, int ev, int n) {
-    if (part < 128 && row_blk == 0 && n < 8) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_span[part][ev][n] = t;
-    }
-}
-__device__ long long g_gtrace[4][512];
-#define GTRACE(ev, n) do { if (part == 0 && row_blk == 0 && gw == 0 && lane == 0 && cta_rank == 0 && (n) < 512) g_gtrace[ev][n] = clock64(); } while (0)
-#define SPAN(ev, n) span_ev(part, row_blk, ev, n)
-#define TRACE(ev, g) trace_ev(part, row_blk, ev, g)
-#define TRACE_CLOCK(ev, g) do { if (part == 0 && row_blk == 0 && (g) < 512) g_trace[ev][g] = (unsigned long long)clock64(); } while (0)
-#else
-#define TRACE(ev, g)
-#define TRACE_CLOCK(ev, g)
-#define SPAN(ev, n)
-#define GTRACE(ev, n)
-#endif
+// single-thread roles: leave at once
+#define WAIT_OR_LEAVE(W, CL, bar, par, code) do { if (!(W).template wait<CL>(bar, par, code)) goto wind_down; } while (0)
+// whole warps (all 32 lanes execute this): leave together, tcgen05.ld/st and shuffles are warp-collective
+#define WAIT_WARP_OR_LEAVE(W, CL, bar, par, code) \
+    do { (W).template wait<CL>(bar, par, code); if (__any_sync(0xffffffffu, (W).aborted)) goto wind_down; } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+// two fp32 -> one 32-bit word of the 16-bit input type (bf16 or fp16), `lo` in the low half
+template <bool FP16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    if (FP16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return pack16<false>(lo, hi); }
 
 // 16 e4m3 values (one uint4) times an fp32 scale -> 16 bf16 (two uint4), one rounding: bf16(fp32(e4m3) * scale).
 // (A conversion-free variant that places the e4m3 magnitude bits into an fp32 word and multiplies by scale * 2^120 is
@@ -284,22 +304,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
     uint32_t o[8];
-#ifdef MLA_DQ_BITS
-    // e4m3 bits placed into an fp32 word (the value times 2^-120, exact, sub-normals included), one multiply by
-    // scale * 2^120: the same product rounded once to fp32, without conversion instructions
-    const float scale120 = scale * 1.329227995784916e36f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        float f[4];
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t x = __byte_perm(w[i], 0, 0x0444 | (b << 12));
-            f[b] = __uint_as_float((x & 0x80000000u) | ((x >> 4) & 0x07f00000u)) * scale120;
-        }
-        o[2 * i] = pack_bf16(f[0], f[1]);
-        o[2 * i + 1] = pack_bf16(f[2], f[3]);
-    }
-#else
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
@@ -309,7 +313,6 @@ __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& 
         o[2 * i] = pack_bf16(f0.x * scale, f0.y * scale);
         o[2 * i + 1] = pack_bf16(f1.x * scale, f1.y * scale);
     }
-#endif
     lo = make_uint4(o[0], o[1], o[2], o[3]);
     hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
@@ -320,11 +323,15 @@ __device__ __forceinline__ const uint8_t* shfl_ptr(const uint8_t* ptr, int src_l
     return reinterpret_cast<const uint8_t*>(((unsigned long long)hi << 32) | lo);
 }
 
-template <int MODE>
+// FP16: q, the cache and out are fp16 instead of bf16 (dense mode only); accumulation is fp32 either way.
+template <int MODE, bool FP16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
 attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const __grid_constant__ CUtensorMap qmap, const Params p) {
     using WalkerT = Walker<MODE>;
+    using L = Lay<MODE>;
+    constexpr int NKS = L::NKS;
+    constexpr bool DENSE = MODE == MODE_DENSE;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();          // 0 = score CTA, 1 = value CTA
@@ -341,7 +348,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (threadIdx.x == 0) {
         // a ring slot is filled by TMA (one arrive.expect_tx + bytes) in dense mode, by the 128 gather threads otherwise
         // ... except the K groups of FP8 decode, which the 256 softmax threads of the score CTA hand over after de-quantising them
-        const uint32_t full_count = MODE == MODE_DENSE ? 1 : (MODE == MODE_SPARSE_DECODE && cta_rank == 0) ? 256 : 128;
+        const uint32_t full_count = DENSE ? 1 : (MODE == MODE_SPARSE_DECODE && cta_rank == 0) ? 256 : 128;
         for (int i = 0; i < NRING; ++i) { mbar_init(smem_addr(&sm.kv_full[i]), full_count); mbar_init(smem_addr(&sm.kv_empty[i]), 1); }
         for (int i = 0; i < NRING; ++i) mbar_init(smem_addr(&sm.raw_full[i]), 128);
         for (int i = 0; i < 2; ++i) {
@@ -361,12 +368,13 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         mbar_init(smem_addr(&sm.ring_released), 256);
         mbar_init(smem_addr(&sm.fin_empty), 128);
         mbar_init(smem_addr(&sm.fin_full), 128);
+        mbar_init(smem_addr(&sm.drain), 1);
         sm.aborted = 0;
         // first use of every P buffer: its arrival and expected byte count are armed here (matters in the value CTA)
         for (int i = 0; i < NPB; ++i)
             mbar_arrive_expect_tx(smem_addr(&sm.p_full[i]), P_SUB_BYTES + ((i & 1) == 0 ? 4 * SIDE_BYTES : 0));
         fence_mbar_init();
-        if (MODE == MODE_DENSE) prefetch_tensormap(cta_rank == 0 ? &kmap : &vmap);
+        if (DENSE) prefetch_tensormap(cta_rank == 0 ? &kmap : &vmap);
         if (p.q_tma && cta_rank == 0) prefetch_tensormap(&qmap);
     }
     if (warp == 1) { tmem_alloc(smem_addr(&sm.tmem_base), 512); tmem_relinquish(); }
@@ -374,32 +382,32 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     __syncthreads();
     tc_fence_after();
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
-    if (threadIdx.x == 0 && cta_rank == 0) SPAN(0, 0);
-#ifdef MLA_TRACE
-    if (threadIdx.x == 0 && cta_rank == 0 && part < 128 && row_blk == 0) { uint32_t smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid)); g_span[part][0][7] = smid; }
-#endif
     const uint32_t tmem = sm.tmem_base;
     // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
     // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
-    using WaiterT = Waiter<MODE == MODE_DENSE>;
-    WaiterT wt(p.status, &sm.aborted, MODE != MODE_DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
+    using WaiterT = Waiter<DENSE>;
+    const uint32_t peer_flag = map_to_cta(smem_addr(&sm.aborted), cta_rank ^ 1u);
+    WaiterT wt(p.status, &sm.aborted, peer_flag, p.wait_limit, !DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
-    // A request's Q (score CTA): nine [rows][64 columns] boxes, chunks 0-6 into the K ring once the
-    // previous request's tiles have left it (the softmax warpgroups move them on to tensor memory and release the
-    // ring), chunks 7 and 8 into their final place.  Large boxes stream several times faster into one SM than
-    // per-thread loads, and the request boundary - where the MMA warp idles - is what this shortens.
+    // what the wind-down has to wait for after an expired wait (thread 0: ring fills and Q boxes it armed)
+    uint32_t fills_armed = 0, q_armed = 0;
+
+    // A request's Q (score CTA): nine [rows][64 columns] boxes into the K ring once the previous request's tiles
+    // have left it (the softmax warpgroups move them on to tensor memory and release the ring); in the gather modes
+    // chunks 7 and 8 go to their final place in shared memory instead.  Large boxes stream several times faster into
+    // one SM than per-thread loads, and the request boundary - where the MMA warp idles - is what this shortens.
     auto issue_q = [&](const Work& w) {
-        if (wt.aborted) return;                    // never arm a barrier whose previous phase may still be open
         const uint32_t bar = smem_addr(&sm.q_landed);
         mbar_arrive_expect_tx(bar, 9u * (uint32_t)p.q_box_bytes);
+        ++q_armed;
         // coordinates: (column, head, query token, request); prefill: a "request" is a query token of the only batch
         const int c1 = MODE == MODE_SPARSE_DECODE ? 0 : MODE == MODE_PREFILL ? row_blk * ROWS : hk * p.g;
         const int c2 = MODE == MODE_SPARSE_DECODE ? (int)blockIdx.y : MODE == MODE_PREFILL ? w.req : row_blk * (ROWS / p.g);
         const int c3 = MODE == MODE_PREFILL ? 0 : w.req;
 #pragma unroll 1
         for (int c = 0; c < 9; ++c) {
-            const uint32_t dst = c < Q_TMEM_CHUNKS ? smem_addr(sm.data + SC_KRING + c * 16384)
-                                                   : smem_addr(sm.data + SC_Q78 + (c - Q_TMEM_CHUNKS) * 16384);
+            const uint32_t dst = c < L::Q_TMEM_CHUNKS ? smem_addr(sm.data + L::SC_KRING + c * 16384)
+                                                      : smem_addr(sm.data + L::SC_Q78 + (c - L::Q_TMEM_CHUNKS) * 16384);
             tma_load_4d(dst, &qmap, bar, c * 64, c1, c2, c3);
         }
     };
@@ -408,60 +416,62 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     // In the sparse modes the CTA has 512 threads that start with 128 registers each; every warpgroup re-sizes its
     // share as the first thing in its own branch (the compiler budgets registers per branch from this).
     if (warp < 4) {
-    if (MODE != MODE_DENSE) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    if (!DENSE) asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ---------------------------------------------------------
-        if (MODE != MODE_DENSE) {
+        if (!DENSE) {
             // sparse modes: the gather warpgroup fills the rings
             if (p.q_tma && cta_rank == 0 && lane == 0) {
                 uint32_t g = 0, nreq = 0;
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     issue_q(w);
-                    wt.wait<false>(&sm.ring_released, nreq & 1, 11);     // (a request without tiles must not be overtaken)
+                    WAIT_OR_LEAVE(wt, false, &sm.ring_released, nreq & 1, 11);     // (a request without tiles must not be overtaken)
                     // The next request's boxes may go out once every MMA of this one has finished with the ring and with
                     // chunks 7, 8 of Q.  A parity wait only means what it says to a thread that has seen every earlier
                     // phase of the barrier, so this thread follows the ring tile by tile.
                     for (int i = 0; i < w.ntiles; ++i, ++g)
-                        for (int grp = 0; grp < 3; ++grp) wt.wait<false>(&sm.kv_empty[grp], g & 1, 13);
+                        for (int grp = 0; grp < 3; ++grp) WAIT_OR_LEAVE(wt, false, &sm.kv_empty[grp], g & 1, 13);
                 }
             }
         } else if (lane == 0) {
-            uint32_t ks = 0;                               // ring slot counter (K groups or V half-pages)
+            uint32_t ks = 0;                               // ring fill counter (K groups or V half-pages)
             uint32_t nreq = 0;
             const int chunk0 = hk * p.head_chunks;         // the kv head's first 64-column chunk in the tensor maps
             for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
                 const int* bt = p.block_table + (int64_t)w.req * p.bt_sb;
+                // a block index beyond the table's width reads no table entry: its keys are zeros
+                auto page_of = [&](int blk) -> int { return (blk < w.blk_end && blk < p.max_blocks) ? __ldg(bt + blk) : oob_page; };
                 // page ids are fetched one tile ahead so the block-table latency stays off the TMA issue path
-                int nxt0 = 0, nxt1 = oob_page;
-                if (w.ntiles > 0) {
-                    nxt0 = __ldg(bt + w.blk_begin);
-                    nxt1 = w.blk_begin + 1 < w.blk_end ? __ldg(bt + w.blk_begin + 1) : oob_page;
-                }
+                int nxt0 = oob_page, nxt1 = oob_page;
+                if (w.ntiles > 0) { nxt0 = page_of(w.blk_begin); nxt1 = page_of(w.blk_begin + 1); }
                 if (p.q_tma && cta_rank == 0) {
-                    // the K ring stages this request's Q first: wait until the previous request's tiles (and every MMA
-                    // that read its Q) are done, send the boxes, and take the ring back once they have been copied out
-                    for (int grp = 0; grp < 3; ++grp) wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 13);
+                    // the K ring stages this request's Q first: wait until the previous request's groups (and every MMA
+                    // that read its Q) are done - slot s is free for its next fill -, send the boxes, and take the ring
+                    // back once they have been copied out
+                    for (uint32_t s = 0; s < (uint32_t)NKS; ++s) {
+                        const uint32_t nf = ks + (uint32_t)(((int)s - (int)(ks % NKS) + NKS) % NKS);      // the next fill that uses slot s
+                        WAIT_OR_LEAVE(wt, false, &sm.kv_empty[s], ((nf / NKS) & 1) ^ 1, 13);
+                    }
                     issue_q(w);
-                    wt.wait<false>(&sm.ring_released, nreq & 1, 11);
+                    WAIT_OR_LEAVE(wt, false, &sm.ring_released, nreq & 1, 11);
                 }
                 for (int i = 0; i < w.ntiles; ++i) {
                     const int page0 = nxt0, page1 = nxt1;
                     if (i + 1 < w.ntiles) {
                         const int nb = w.blk_begin + 2 * (i + 1);
-                        nxt0 = __ldg(bt + nb);
-                        nxt1 = nb + 1 < w.blk_end ? __ldg(bt + nb + 1) : oob_page;
+                        nxt0 = page_of(nb);
+                        nxt1 = page_of(nb + 1);
                     }
                     if (cta_rank == 0) {
                         for (int grp = 0; grp < 3; ++grp, ++ks) {
-                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 1);
-                            if (wt.aborted) continue;      // never arm a barrier whose previous phase may still be open
-                            if (grp == 0) TRACE(0, ks / 3);
-                            if (grp == 2) TRACE(7, ks / 3);
-                            const uint32_t bar = smem_addr(&sm.kv_full[grp]);
+                            const uint32_t slot = ks % NKS;
+                            WAIT_OR_LEAVE(wt, false, &sm.kv_empty[slot], ((ks / NKS) & 1) ^ 1, 1);
+                            const uint32_t bar = smem_addr(&sm.kv_full[slot]);
                             mbar_arrive_expect_tx(bar, K_GROUP_BYTES);
-                            const uint32_t dst = smem_addr(sm.data + SC_KRING + grp * K_GROUP_BYTES);
+                            fills_armed = ks + 1;
+                            const uint32_t dst = smem_addr(sm.data + L::SC_KRING + slot * K_GROUP_BYTES);
                             // one box per page: 3 chunks x 64 tokens land as [8-token group][chunk][8 x 128 B]
                             tma_load_5d(dst, &kmap, bar, 0, 0, chunk0 + grp * 3, 0, page0);
                             tma_load_5d(dst + K_GROUP_BYTES / 2, &kmap, bar, 0, 0, chunk0 + grp * 3, 0, page1);
@@ -471,10 +481,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int page = h ? page1 : page0;
                             for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
-                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
-                                if (wt.aborted) continue;  // never arm a barrier whose previous phase may still be open
+                                WAIT_OR_LEAVE(wt, false, &sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 101);
                                 const uint32_t bar = smem_addr(&sm.kv_full[slot]);
                                 mbar_arrive_expect_tx(bar, V_SLOT_BYTES);
+                                fills_armed = ks + 1;
                                 const uint32_t dst = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES);
                                 // one box: 4 chunks x 64 tokens as [8-token group][chunk][8 x 128 B]
                                 tma_load_5d(dst, &vmap, bar, 0, 0, chunk0 + nh * 4, 0, page);
@@ -488,81 +498,76 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // ---------------- MMA issuer -----------------------------------------------------------------------
         if (lane == 0) {
             uint32_t g = 0, ks = 0, nreq = 0;
-            (void)ks;
             if (cta_rank == 0) {
-                constexpr uint32_t idesc = make_idesc_bf16(ROWS, 128, false);
-                const uint32_t q78_lo = sw128_desc_lo(smem_addr(sm.data + SC_Q78), 16);
-                const uint32_t kring_lo = sw128_desc_lo(smem_addr(sm.data + SC_KRING), 16);
+                constexpr uint32_t idesc = make_idesc_16(ROWS, 128, false, FP16);
+                const uint32_t q78_lo = sw128_desc_lo(smem_addr(sm.data + L::SC_Q78), 16);
+                const uint32_t kring_lo = sw128_desc_lo(smem_addr(sm.data + L::SC_KRING), 16);
                 const uint32_t kv_empty0 = smem_addr(&sm.kv_empty[0]);
                 const uint32_t kv_full0 = smem_addr(&sm.kv_full[0]);
+                uint32_t slot = 0, par = 0;                 // ring position of the next group: slot = ks mod NKS, par = (ks / NKS) & 1
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
-                    wt.wait<false>(&sm.q_ready, nreq & 1, 2);
-                    SPAN(1, nreq);
+                    WAIT_OR_LEAVE(wt, false, &sm.q_ready, nreq & 1, 2);
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
-                        const uint32_t sb = g & 1;
-                        wt.wait<false>(&sm.s_empty[sb], ((g >> 1) & 1) ^ 1, 4);
+                        const uint32_t sb = L::S_BUFS == 2 ? (g & 1) : 0;
+                        const uint32_t s_par = L::S_BUFS == 2 ? ((g >> 1) & 1) : (g & 1);
+                        WAIT_OR_LEAVE(wt, false, &sm.s_empty[sb], s_par ^ 1, 4);
                         tc_fence_after();
-                        TRACE(1, g);
-                        TRACE_CLOCK(13, g);
-                        const uint32_t d_tmem = tmem + TM_S + sb * 128;
-                        // Group j of every tile lives in ring slot j, parity = tile parity.  Descriptors advance by
-                        // 32-bit adds only and the loop is fully unrolled: one thread issues everything, so its
-                        // instruction latency is the issue rate.
+                        const uint32_t d_tmem = tmem + L::TM_S + sb * 128;
+                        // Descriptors advance by 32-bit adds only and the loop is fully unrolled: one thread issues
+                        // everything, so its instruction latency is the issue rate.
                         constexpr uint32_t hi = sw128_desc_hi(1024);
                         // K operand: the gather modes store a tile as 9 chunks of [128 tokens][128 B]; the dense mode's
                         // TMA boxes interleave the 3 chunks of a ring group inside every 8-token group.
-                        constexpr uint32_t hi_k = sw128_desc_hi(MODE == MODE_DENSE ? 3 * 1024 : 1024);
+                        constexpr uint32_t hi_k = sw128_desc_hi(DENSE ? 3 * 1024 : 1024);
                         // The probe of the next group's barrier is issued before this group's MMAs so that its
                         // latency hides behind them (the MMA queue is shallow: time the issuing thread spends
                         // waiting is time the tensor pipe idles).
-                        bool ready = mbar_try_wait(kv_full0, g & 1);
+                        bool ready = mbar_try_wait(kv_full0 + slot * 8, par);
 #pragma unroll
                         for (int grp = 0; grp < 3; ++grp) {
-                            if (!ready) wt.wait<false>(&sm.kv_full[grp], g & 1, 3);
+                            if (!ready) WAIT_OR_LEAVE(wt, false, &sm.kv_full[slot], par, 3);
                             tc_fence_after();
-                            if (grp == 0) TRACE(8, g);
-                            if (grp == 2) TRACE(14, g);
-                            if (grp < 2) ready = mbar_try_wait(kv_full0 + (grp + 1) * 8, g & 1);
+                            const uint32_t cur = slot;
+                            if (++slot == (uint32_t)NKS) { slot = 0; par ^= 1; }
+                            if (grp < 2) ready = mbar_try_wait(kv_full0 + slot * 8, par);
+                            const uint32_t grp_lo = kring_lo + cur * (K_GROUP_BYTES >> 4);
 #pragma unroll
                             for (int c = 0; c < 3; ++c) {
                                 const int j = grp * 3 + c;
-                                const uint32_t b_lo = MODE == MODE_DENSE ? kring_lo + grp * (K_GROUP_BYTES >> 4) + c * (1024 >> 4)
-                                                                         : kring_lo + j * (K_CHUNK_BYTES >> 4);
+                                const uint32_t b_lo = DENSE ? grp_lo + c * (1024 >> 4) : grp_lo + c * (K_CHUNK_BYTES >> 4);
 #pragma unroll
                                 for (int k4 = 0; k4 < 4; ++k4) {
                                     const uint32_t acc = (j > 0 || k4 > 0) ? 1u : 0u;
-                                    if (j < Q_TMEM_CHUNKS) mma_ts_lohi(d_tmem, tmem + TM_Q + j * 32 + k4 * 8, b_lo + k4 * 2, hi_k, idesc, acc);
-                                    else mma_ss_lohi(d_tmem, q78_lo + (j - Q_TMEM_CHUNKS) * (16384 >> 4) + k4 * 2, hi, b_lo + k4 * 2, hi_k, idesc, acc);
+                                    if (j < L::Q_TMEM_CHUNKS) mma_ts_lohi(d_tmem, tmem + L::TM_Q + j * 32 + k4 * 8, b_lo + k4 * 2, hi_k, idesc, acc);
+                                    else mma_ss_lohi(d_tmem, q78_lo + (j - L::Q_TMEM_CHUNKS) * (16384 >> 4) + k4 * 2, hi, b_lo + k4 * 2, hi_k, idesc, acc);
                                 }
                             }
-                            tc_commit(kv_empty0 + grp * 8);
+                            tc_commit(kv_empty0 + cur * 8);
                         }
                         tc_commit(smem_addr(&sm.s_full[sb]));
-                        TRACE(2, g);
                     }
-                    SPAN(2, nreq);
                 }
             } else {
-                constexpr uint32_t idesc = make_idesc_bf16(ROWS, 256, true);
+                constexpr uint32_t idesc = make_idesc_16(ROWS, 256, true, FP16);
                 // V operand (MN-major): LBO = stride between 64-dim chunks, SBO = stride between 8-token groups.  Gather
                 // modes: 4 chunks of [64 tokens][128 B]; dense mode: chunks interleaved inside every 8-token group.
-                constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(MODE == MODE_DENSE ? 4 * 1024 : 1024);
-                constexpr uint32_t v_kstep = (MODE == MODE_DENSE ? 2 * 4096 : 2 * 1024) >> 4;      // 16 tokens
+                constexpr uint32_t hi_a = sw128_desc_hi(1024), hi_b = sw128_desc_hi(DENSE ? 4 * 1024 : 1024);
+                constexpr uint32_t v_kstep = (DENSE ? 2 * 4096 : 2 * 1024) >> 4;      // 16 tokens
                 const uint32_t p_lo = sw128_desc_lo(smem_addr(sm.data + VA_P), 16);
-                const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), MODE == MODE_DENSE ? 1024 : BOX_BYTES);
+                const uint32_t vring_lo = sw128_desc_lo(smem_addr(sm.data + VA_VRING), DENSE ? 1024 : BOX_BYTES);
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         for (int h = 0; h < 2; ++h) {
                             const uint32_t pb = (g & 1) * 2 + h, pph = (g >> 1) & 1;
-                            wt.wait<true>(&sm.p_full[pb], pph, 104);
-                            wt.wait<false>(&sm.corr_done[pb], pph, 105);
+                            WAIT_OR_LEAVE(wt, true, &sm.p_full[pb], pph, 104);
+                            WAIT_OR_LEAVE(wt, false, &sm.corr_done[pb], pph, 105);
                             const uint32_t a_lo = p_lo + pb * (P_SUB_BYTES >> 4);
 #pragma unroll
                             for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
-                                wt.wait<false>(&sm.kv_full[slot], (ks / NVS) & 1, 103);
+                                WAIT_OR_LEAVE(wt, false, &sm.kv_full[slot], (ks / NVS) & 1, 103);
                                 if (nh == 0) fence_proxy_async_smem();
                                 tc_fence_after();
                                 const uint32_t b_lo = vring_lo + slot * (V_SLOT_BYTES >> 4);
@@ -579,45 +584,27 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
     } else if (warp == 2 || warp == 3) {
-#ifdef MLA_TRACE_KLAND
-        if (cta_rank == 0 && lane == 0) {      // debug: when does the data of K chunk 0 / 8 of every tile land
-            uint32_t ks = 0;
-            for (WalkerT wk(p, part); wk.valid(); wk.next()) {
-                const Work w = wk.get();
-                for (int i = 0; i < w.ntiles; ++i)
-                    for (int j = 0; j < 9; ++j, ++ks) {
-                        wt.wait<false>(&sm.kv_full[ks % NKS], (ks / NKS) & 1, 99);
-                        if (j == 0) TRACE(9, 2 * (ks / 9));
-                        if (j == 8) TRACE(9, 2 * (ks / 9) + 1);
-                    }
-            }
-        }
-#endif
         // ---------------- score CTA: push finished P pages (and, with page 0, the rescale factors) to the value CTA
         if (cta_rank == 0 && lane == 0) {
             const int half = warp - 2;
             uint32_t g = 0;
-            const uint32_t src_p = smem_addr(sm.data + SC_STAGE + half * 4 * 4096);
-            const uint32_t src_side = smem_addr(sm.data + SC_SIDE);
+            const uint32_t src_p = smem_addr(sm.data + L::SC_STAGE + half * 4 * 4096);
+            const uint32_t src_side = smem_addr(sm.data + L::SC_SIDE);
             const uint32_t remote_p = map_to_cta(smem_addr(sm.data + VA_P), 1);
-            const uint32_t remote_side = map_to_cta(smem_addr(&sm.side[0][0][0]), 1);
+            const uint32_t remote_side = map_to_cta(smem_addr(sm.data + VA_SIDE), 1);
             uint32_t remote_p_full[NPB];
             for (int i = 0; i < NPB; ++i) remote_p_full[i] = map_to_cta(smem_addr(&sm.p_full[i]), 1);
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     const uint32_t pb = (g & 1) * 2 + half;
-                    wt.wait<false>(&sm.stage_full[half], g & 1, 9);
-                    wt.wait<true>(&sm.p_empty[pb], ((g >> 1) & 1) ^ 1, 6);   // that P buffer of the value CTA has been consumed
-                    if (half == 0) { TRACE(5, g); TRACE_CLOCK(9, g); }
+                    WAIT_OR_LEAVE(wt, false, &sm.stage_full[half], g & 1, 9);
+                    WAIT_OR_LEAVE(wt, true, &sm.p_empty[pb], ((g >> 1) & 1) ^ 1, 6);   // that P buffer of the value CTA has been consumed
                     // p_full[pb] is armed (arrival + expected bytes) by the value CTA itself: a remote arrive with
                     // release semantics costs over a microsecond, the copies below only count bytes.
-                    if (half == 0) TRACE_CLOCK(10, g);
                     bulk_copy_to_cluster(remote_p + pb * P_SUB_BYTES, src_p, P_SUB_BYTES, remote_p_full[pb]);
-                    if (half == 0) TRACE_CLOCK(11, g);
                     if (half == 0)
                         bulk_copy_to_cluster(remote_side + (g & 1) * 4 * SIDE_BYTES, src_side, 4 * SIDE_BYTES, remote_p_full[pb]);
-                    if (half == 0) { TRACE_CLOCK(12, g); TRACE(6, g); }
                 }
             }
         }
@@ -631,9 +618,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     for (int h = 0; h < 2; ++h) {
                         const uint32_t pb = (g & 1) * 2 + h;
-                        wt.wait<false>(&sm.pv_done[pb], (g >> 1) & 1, 106);
+                        WAIT_OR_LEAVE(wt, false, &sm.pv_done[pb], (g >> 1) & 1, 106);
                         // arm the buffer's barrier for its next use, then let the score CTA refill it
-                        if (wt.aborted) continue;            // never arm a barrier whose previous phase may be open
                         mbar_arrive_expect_tx(smem_addr(&sm.p_full[pb]), P_SUB_BYTES + (h == 0 ? 4 * SIDE_BYTES : 0));
                         mbar_arrive_remote_relaxed(remote_p_empty[pb]);
                     }
@@ -641,7 +627,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
     }
-    } else if (MODE != MODE_DENSE && warp >= 12) {
+    } else if (!DENSE && warp >= 12) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
         // ---------------- gather warpgroup (sparse modes): fills the K ring (score CTA) / V ring (value CTA) by index ----
         // Every warp owns a block of tokens; one cp.async instruction of the warp copies consecutive 16-byte pieces of
@@ -650,7 +636,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         // barrier counts one arrival per thread, made by the copy engine when that thread's copies have landed.
         const int gw = warp - 12;                                 // warp inside the gather warpgroup
         uint32_t ks = 0, g = 0, nreq_p = 0;
-        uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + SC_MASK);
+        uint32_t* kmask = reinterpret_cast<uint32_t*>(sm.data + L::SC_MASK);
         if (MODE == MODE_SPARSE_DECODE) {
             // FP8 records: index -> (page, offset) -> 656-byte record = 512 e4m3 | 4 fp32 scales | 64 bf16 RoPE.
             // A "piece" is 16 e4m3 values (16 bytes) that de-quantise (one rounding: bf16(fp32(e4m3) * scale)) into two
@@ -671,12 +657,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             bool ring_lent = false;                                       // the K ring first stages every request's Q
             uint32_t nreq_g = 0;
             float4 sc_cur = make_float4(0.f, 0.f, 0.f, 0.f);
-            const uint32_t kring = smem_addr(sm.data + SC_KRING);
+            const uint32_t kring = smem_addr(sm.data + L::SC_KRING);
             const uint32_t vring = smem_addr(sm.data + VA_VRING);
             for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq_g) {
                 const Work w = wk.get();
                 ring_lent = p.q_tma && cta_rank == 0;
-                if (ring_lent && w.ntiles == 0) wt.wait<false>(&sm.ring_released, nreq_g & 1, 211);   // follow every phase
+                if (ring_lent && w.ntiles == 0) WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_g & 1, 211);   // follow every phase
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
                 const int* idx1 = p.stopk[1] ? p.sidx[1] + (int64_t)w.req * p.sidx_sb[1] + (int64_t)tq * p.sidx_ss[1] : nullptr;
                 // index -> record address in two steps, so that the index of a tile can be loaded two tiles ahead and
@@ -711,17 +697,15 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         // comes before the prefetch loads are issued: it would wait for them)
                         const uint32_t bal = __ballot_sync(0xffffffffu, rec != nullptr);
                         if (lane == 0) kmask[(g & 3) * 4 + gw] = bal;
-                        reinterpret_cast<float4*>(sm.data + SC_SCALES)[(g & 1) * ROWS + tok] = sc_cur;
+                        reinterpret_cast<float4*>(sm.data + L::SC_SCALES)[(g & 1) * ROWS + tok] = sc_cur;
                         __threadfence_block();
                         rec_next = rec_of(myblk + 2 * (i + 1), id_next);
                         sc_next = scales_of(rec_next);
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
-                        if (ring_lent) { wt.wait<false>(&sm.ring_released, nreq_g & 1, 211); ring_lent = false; }
+                        if (ring_lent) { WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_g & 1, 211); ring_lent = false; }
 #pragma unroll 1
                         for (int grp = 0; grp < 3; ++grp, ++ks) {
-                            GTRACE(0, ks);
-                            wt.wait<false>(&sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
-                            GTRACE(1, ks);
+                            WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
                             // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row.  A copy
                             // instruction costs the warp the same whatever its active lanes: each one serves two rows.
                             const int per_row = grp < 2 ? 12 : 16;
@@ -741,7 +725,6 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             }
                             // the softmax warpgroups expand the pieces in place once they have landed
                             cp_async_arrive_noinc(smem_addr(&sm.raw_full[grp]));
-                            GTRACE(2, ks);
                         }
                     }
                 } else {
@@ -759,7 +742,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #pragma unroll 1
                             for (int nh = 0; nh < 2; ++nh, ++ks) {
                                 const uint32_t slot = ks % NVS;
-                                wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
+                                WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
                                 // copy: 16 raw pieces per row (dims nh*256 .. nh*256+255); one instruction serves two rows
                                 const int ql = lane & 15, sub = lane >> 4;
                                 const int q = nh * 16 + ql;
@@ -781,7 +764,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq_p) {
             const Work w = wk.get();
             bool ring_lent = p.q_tma && cta_rank == 0;          // the K ring first stages this query token's Q
-            if (ring_lent && w.ntiles == 0) wt.wait<false>(&sm.ring_released, nreq_p & 1, 211);        // follow every phase
+            if (ring_lent && w.ntiles == 0) WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_p & 1, 211);        // follow every phase
             const int* idx = p.indices + (int64_t)w.req * p.idx_ss;
             // the index of a tile's token is loaded one tile ahead (a load that is used at once costs its latency)
             int id_next = -1;
@@ -803,13 +786,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     // four rows by a third: 72 instructions per 32 rows.  The ring barriers still count per group of 3
                     // chunks: every group's arrival is issued once all copies that touch it have been issued.
                     const uint32_t par = ((ks / NKS) & 1) ^ 1;
-                    const uint32_t ring0 = smem_addr(sm.data + SC_KRING) + gw * 32 * 128;
+                    const uint32_t ring0 = smem_addr(sm.data + L::SC_KRING) + gw * 32 * 128;
                     const int c = lane & 7;
-                    GTRACE(0, ks);
-                    if (ring_lent) { wt.wait<false>(&sm.ring_released, nreq_p & 1, 211); ring_lent = false; }
-                    wt.wait<false>(&sm.kv_empty[0], par, 201);
-                    wt.wait<false>(&sm.kv_empty[1], par, 201);
-                    GTRACE(1, ks);
+                    if (ring_lent) { WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_p & 1, 211); ring_lent = false; }
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[0], par, 201);
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[1], par, 201);
                     {
                         const uint32_t dst0 = ring0 + (lane >> 3) * K_CHUNK_BYTES;
 #pragma unroll 8
@@ -820,8 +801,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         }
                     }
                     cp_async_arrive_noinc(smem_addr(&sm.kv_full[0]));
-                    GTRACE(2, ks);
-                    wt.wait<false>(&sm.kv_empty[2], par, 201);
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[2], par, 201);
                     {
                         const uint32_t dst0 = ring0 + (4 + (lane >> 3)) * K_CHUNK_BYTES;
 #pragma unroll 8
@@ -852,7 +832,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         const int row_id = (id >= 0 && id < p.s_kv) ? id : -1;
                         for (int nh = 0; nh < 2; ++nh, ++ks) {
                             const uint32_t slot = ks % NVS;
-                            wt.wait<false>(&sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
+                            WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[slot], ((ks / NVS) & 1) ^ 1, 202);
                             const int box = lane >> 3, c = lane & 7;
                             const uint32_t dst0 = smem_addr(sm.data + VA_VRING + slot * V_SLOT_BYTES) + box * BOX_BYTES + gw * 16 * 128;
 #pragma unroll 8
@@ -868,7 +848,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             }
         }
     } else {
-        if (MODE != MODE_DENSE) asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
+        if (!DENSE) asm volatile("setmaxnreg.inc.sync.aligned.u32 160;");
         const int wq = warp & 3;                                  // TMEM lane quarter of this warp
         const int half = (warp - 4) >> 2;                         // score CTA: page of the tile this warpgroup owns
         const int r = wq * 32 + lane;                             // row inside the block = TMEM lane
@@ -882,31 +862,33 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
         if (cta_rank == 0) {
             // ---------------- softmax warpgroups of the score CTA --------------------------------------------
-            uint8_t* stage = sm.data + SC_STAGE + (half * 4 + wq) * 4096;
-            float* side_src = reinterpret_cast<float*>(sm.data + SC_SIDE + wq * SIDE_BYTES);
-            float* xmax = reinterpret_cast<float*>(sm.data + SC_XMAX);
-            const uint32_t remote_fin_l = map_to_cta(smem_addr(&sm.fin_l[r]), 1);
-            const uint32_t remote_fin_m = map_to_cta(smem_addr(&sm.fin_m[r]), 1);
-            const uint32_t remote_fin_mt = map_to_cta(smem_addr(&sm.fin_mt[r]), 1);
+            // These 256 threads meet at a named barrier every tile, so none of them may leave alone: a thread whose
+            // wait ran out keeps walking (its later waits return at once, it arrives nowhere and stores nothing
+            // outside its own staging) until the next such barrier, which carries the flag to everyone (bar.red.or);
+            // behind it all 256 leave together.
+            uint8_t* stage = sm.data + L::SC_STAGE + (half * 4 + wq) * 4096;
+            float* side_src = reinterpret_cast<float*>(sm.data + L::SC_SIDE + wq * SIDE_BYTES);
+            float* xmax = reinterpret_cast<float*>(sm.data + L::SC_XMAX);
+            const uint32_t remote_fin = map_to_cta(smem_addr(sm.data + VA_FIN), 1) + (uint32_t)r * 4u;
             const uint32_t remote_fin_full = map_to_cta(smem_addr(&sm.fin_full), 1);
             // FP8 decode: these 256 threads also de-quantise the K tiles in place (two threads per token row, every other
             // 16-value piece each), one tile ahead of the softmax they compute: tile g + 1 is converted before the scores
             // of tile g are awaited, so the MMA warp has the next tile while this warpgroup is busy with the softmax.
             uint32_t conv_tile = 0;
-            WaiterT wt_fast(p.status, &sm.aborted);                   // conversion sits on the MMA warp's critical path: no sleeping
+            WaiterT wt_fast(p.status, &sm.aborted, peer_flag, p.wait_limit);     // conversion sits on the MMA warp's critical path: no sleeping
             auto convert_tile = [&](const uint32_t tile) {
                 const int sw = r & 7;
                 float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
                 for (int grp = 0; grp < 3; ++grp) {
-                    wt_fast.wait<false>(&sm.raw_full[grp], tile & 1, 205);
+                    if (!wt_fast.template wait<false>(&sm.raw_full[grp], tile & 1, 205)) { wt.aborted = true; return; }
                     // the tile's scales were stored (and fenced) by the gather warps before they issued its first copies
-                    if (grp == 0) sc = reinterpret_cast<const float4*>(sm.data + SC_SCALES)[(tile & 1) * ROWS + r];
+                    if (grp == 0) sc = reinterpret_cast<const float4*>(sm.data + L::SC_SCALES)[(tile & 1) * ROWS + r];
                     const int nconv = grp < 2 ? 3 : 2;                 // group 2: chunks 6, 7 and the RoPE chunk (copied as it is)
 #pragma unroll 1
                     for (int cj = 0; cj < nconv; ++cj) {
                         const int j = grp * 3 + cj, sg = j >> 1;
-                        uint8_t* rowp = sm.data + SC_KRING + j * K_CHUNK_BYTES + r * 128;
+                        uint8_t* rowp = sm.data + L::SC_KRING + j * K_CHUNK_BYTES + r * 128;
                         const float scale = sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w;
                         uint4 raw[2];
 #pragma unroll
@@ -926,34 +908,35 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             };
             for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                 const Work w = wk.get();
-                // ---- Q row -> A operand: chunks 0..6 to tensor memory (2 bf16 per 32-bit column), chunks 7, 8 to shared
-                // memory (K-major, 128-byte swizzle).  Warpgroup 0 takes chunks 0-3 and 7, warpgroup 1 chunks 4-6 and 8.
+                // ---- Q row -> A operand: chunks [0, Q_TMEM_CHUNKS) to tensor memory (2 x 16 bit per 32-bit column), in the
+                // gather modes chunks 7, 8 to shared memory (K-major, 128-byte swizzle).  Warpgroup 0 takes chunks
+                // [0, Q_SPLIT) (and 7), warpgroup 1 the others (and 8).
                 // Every MMA that read the previous request's Q has completed: this thread saw s_full of its last tile.
                 {
                     const __nv_bfloat16* qrow = MODE == MODE_PREFILL
                         ? p.q + (int64_t)w.req * p.q_ss + (int64_t)hd * p.q_sh
                         : p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
-                    const int c_begin = half ? 4 : 0, c_end = half ? 7 : 4, c_smem = half ? 8 : 7;
+                    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT, c_smem = half ? 8 : 7;
                     if (p.q_tma) {
-                        // Q arrived as TMA boxes: chunks 7 and 8 are in place, chunks 0-6 wait in the K ring as
-                        // [row][128 B] with the 128-byte swizzle
-                        wt.wait<false>(&sm.q_landed, nreq & 1, 12);
+                        // Q arrived as TMA boxes: in the gather modes chunks 7 and 8 are in place; the others wait in the K
+                        // ring as [row][128 B] with the 128-byte swizzle
+                        wt.template wait<false>(&sm.q_landed, nreq & 1, 12);
 #pragma unroll 1
                         for (int c = c_begin; c < c_end; ++c) {
-                            const uint8_t* qsrc = sm.data + SC_KRING + c * 16384 + r * 128;
+                            const uint8_t* qsrc = sm.data + L::SC_KRING + c * 16384 + r * 128;
                             uint32_t v[32];
 #pragma unroll
                             for (int ch = 0; ch < 8; ++ch) {
                                 const uint4 x = *reinterpret_cast<const uint4*>(qsrc + ((ch ^ (r & 7)) << 4));
                                 v[4 * ch] = x.x; v[4 * ch + 1] = x.y; v[4 * ch + 2] = x.z; v[4 * ch + 3] = x.w;
                             }
-                            tmem_st32(tlane + TM_Q + c * 32, v);
+                            tmem_st32(tlane + L::TM_Q + c * 32, v);
                         }
                         tmem_wait_st();
-                        mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
+                        if (!wt.aborted) mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
                     } else
 #pragma unroll 1
-                    for (int c = c_begin; c <= c_end; ++c) {
+                    for (int c = c_begin; c < c_end + (DENSE ? 0 : 1); ++c) {
                         const int chunk = c < c_end ? c : c_smem;
                         uint32_t v[32];
                         if (row_ok) {
@@ -968,9 +951,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             for (int i = 0; i < 32; ++i) v[i] = 0u;
                         }
                         if (c < c_end) {
-                            tmem_st32(tlane + TM_Q + chunk * 32, v);
+                            tmem_st32(tlane + L::TM_Q + chunk * 32, v);
                         } else {
-                            uint8_t* qdst = sm.data + SC_Q78 + (chunk - Q_TMEM_CHUNKS) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+                            uint8_t* qdst = sm.data + L::SC_Q78 + (chunk - L::Q_TMEM_CHUNKS) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
 #pragma unroll
                             for (int ch = 0; ch < 8; ++ch)
                                 *reinterpret_cast<uint4*>(qdst + ((ch ^ (r & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
@@ -979,34 +962,34 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     tmem_wait_st();
                     fence_proxy_async_smem();
                     tc_fence_before();
-                    mbar_arrive(smem_addr(&sm.q_ready));
+                    if (!wt.aborted) mbar_arrive(smem_addr(&sm.q_ready));
                 }
                 // first key position this row must NOT see (causal limit, and the end of this partition's range)
                 const int limit = min(p.causal ? w.seqlen - (p.s_q - 1 - t) : w.seqlen, w.blk_end * PAGE);
                 float m_run = -INFINITY, l_run = 0.f, m_true = -INFINITY;
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
-                    const uint32_t sb = g & 1, ph = (g >> 1) & 1;
+                    const uint32_t sb = L::S_BUFS == 2 ? (g & 1) : 0;
+                    const uint32_t ph = L::S_BUFS == 2 ? ((g >> 1) & 1) : (g & 1);
                     if (MODE == MODE_SPARSE_DECODE)
                         // one tile ahead, but never into the next request: its first tile can only be gathered after
                         // these threads have moved that request's Q out of the K ring
-                        while (conv_tile <= g + 1 && conv_tile < g + (uint32_t)(w.ntiles - i)) convert_tile(conv_tile++);
-                    wt.wait<false>(&sm.s_full[sb], ph, 5);
+                        while (!wt.aborted && conv_tile <= g + 1 && conv_tile < g + (uint32_t)(w.ntiles - i)) convert_tile(conv_tile++);
+                    wt.template wait<false>(&sm.s_full[sb], ph, 5);
                     tc_fence_after();
-                    if (threadIdx.x == 128) TRACE(3, g);
                     uint32_t s[64];
                     {
                         uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[0]);
                         uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&s[32]);
-                        tmem_ld32(tlane + TM_S + sb * 128 + half * 64, lo);
-                        tmem_ld32(tlane + TM_S + sb * 128 + half * 64 + 32, hi);
+                        tmem_ld32(tlane + L::TM_S + sb * 128 + half * 64, lo);
+                        tmem_ld32(tlane + L::TM_S + sb * 128 + half * 64 + 32, hi);
                     }
                     tmem_wait_ld();
                     tc_fence_before();
-                    mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
+                    if (!wt.aborted) mbar_arrive(smem_addr(&sm.s_empty[sb]));          // the MMA warp may overwrite this S accumulator
 
-                    if (MODE != MODE_DENSE) {
+                    if (!DENSE) {
                         // validity bits of the gathered tokens: token 32w + l of the tile is bit l of word w
-                        const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + SC_MASK) + (g & 3) * 4 + half * 2;
+                        const uint32_t* km = reinterpret_cast<const uint32_t*>(sm.data + L::SC_MASK) + (g & 3) * 4 + half * 2;
                         const uint32_t m0 = km[0], m1 = km[1];
                         if ((m0 & m1) != 0xffffffffu) {
 #pragma unroll
@@ -1028,9 +1011,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         mx1 = fmaxf(mx1, __uint_as_float(s[c + 1]));
                     }
                     float mx = fmaxf(mx0, mx1);
-                    // the row maximum over both pages of the tile
+                    // the row maximum over both pages of the tile; the barrier also carries the abort flag
                     xmax[((g & 1) * 2 + half) * ROWS + r] = mx;
-                    named_bar_sync(1, 256);
+                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
                     mx = fmaxf(mx, xmax[((g & 1) * 2 + (half ^ 1)) * ROWS + r]);
                     mx *= p.scale_log2;                                // scale > 0: max commutes with scaling
                     m_true = fmaxf(m_true, mx);
@@ -1052,15 +1035,14 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         const float e0 = ex2(fmaf(__uint_as_float(s[c]), p.scale_log2, neg_m));
                         const float e1 = ex2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, neg_m));
                         sum0 += e0; sum1 += e1;
-                        pk[c >> 1] = pack_bf16(e0, e1);
+                        pk[c >> 1] = pack16<FP16>(e0, e1);
                     }
                     l_run += sum0 + sum1;
                     const bool any_resc = __any_sync(0xffffffffu, resc);
-                    if (threadIdx.x == 128) TRACE(4, g);
 
                     // staging of this warp is free once the previous tile's copy has landed in the value CTA
-                    wt.wait<true>(&sm.stage_free[half], (g & 1) ^ 1, 8);
-                    {
+                    wt.template wait<true>(&sm.stage_free[half], (g & 1) ^ 1, 8);
+                    if (!wt.aborted) {
                         uint8_t* prow = stage + (lane >> 3) * 1024 + (lane & 7) * 128;
 #pragma unroll
                         for (int ch = 0; ch < 8; ++ch)
@@ -1069,25 +1051,28 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             side_src[lane] = factor;
                             if (lane == 0) reinterpret_cast<uint32_t*>(side_src)[32] = any_resc ? 1u : 0u;
                         }
+                        fence_proxy_async_smem();                          // staging is read by the bulk-copy engine
+                        mbar_arrive(smem_addr(&sm.stage_full[half]));      // the sender warp pushes it to the value CTA
                     }
-                    fence_proxy_async_smem();                          // staging is read by the bulk-copy engine
-                    mbar_arrive(smem_addr(&sm.stage_full[half]));      // the sender warp pushes it to the value CTA
                 }
                 // final statistics of this request for the epilogue in the value CTA: warpgroup 1 hands its row sums to
-                // warpgroup 0, which sends sum, running maximum and true maximum
+                // warpgroup 0, which sends sum, running maximum and true maximum.  (Dense mode has no spare shared memory:
+                // the hand-over uses the row-maximum slots of the tile parity that is not in use.)
                 {
-                    float* lsum = reinterpret_cast<float*>(sm.data + SC_LSUM);
+                    float* lsum = DENSE ? xmax + ((g & 1) * 2) * ROWS : reinterpret_cast<float*>(sm.data + L::SC_LSUM);
                     if (half == 1) lsum[r] = l_run;
-                    named_bar_sync(1, 256);
+                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
                     if (half == 0) l_run += lsum[r];
-                    named_bar_sync(1, 256);
+                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
                 }
                 if (half == 0) {
-                    wt.wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
-                    st_cluster_f32(remote_fin_l, l_run);
-                    st_cluster_f32(remote_fin_m, m_run);
-                    st_cluster_f32(remote_fin_mt, m_true);
-                    mbar_arrive_remote(remote_fin_full);
+                    wt.template wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
+                    if (!wt.aborted) {
+                        st_cluster_f32(remote_fin, l_run);
+                        st_cluster_f32(remote_fin + ROWS * 4, m_run);
+                        st_cluster_f32(remote_fin + 2 * ROWS * 4, m_true);
+                        mbar_arrive_remote(remote_fin_full);
+                    }
                 }
             }
         } else if (warp < 8) {
@@ -1095,8 +1080,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const uint32_t remote_fin_empty = map_to_cta(smem_addr(&sm.fin_empty), 0);
             const uint32_t remote_stage_free0 = map_to_cta(smem_addr(&sm.stage_free[0]), 0);
             const uint32_t remote_stage_free1 = map_to_cta(smem_addr(&sm.stage_free[1]), 0);
+            const float* fin = reinterpret_cast<const float*>(sm.data + VA_FIN);
             uint32_t vs = 0;                                          // V ring slot counter
-            // bf16 output rows start on 32-byte boundaries: 256-bit stores may be used (decode modes; measured in one run
+            // 16-bit output rows start on 32-byte boundaries: 256-bit stores may be used (decode modes; measured in one run
             // against 16-byte stores: dense 0.2134 -> 0.2088 ms, FP8 decode 0.1107 -> 0.1090 ms, prefill 3.348 -> 3.379 ms,
             // so prefill keeps the 16-byte stores)
             const bool wide_out = MODE != MODE_PREFILL && (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 &&
@@ -1106,16 +1092,16 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 for (int i = 0; i < w.ntiles; ++i, ++g) {
                     for (int h = 0; h < 2; ++h, vs += 2) {
                         const uint32_t pb = (g & 1) * 2 + h, ph = (g >> 1) & 1;
-                        wt.wait<true>(&sm.p_full[pb], ph, 107);
+                        WAIT_WARP_OR_LEAVE(wt, true, &sm.p_full[pb], ph, 107);
                         if (threadIdx.x == 128) {
                             mbar_arrive_remote_relaxed(h ? remote_stage_free1 : remote_stage_free0);   // the copy has landed
                         }
                         if (h == 0 && i > 0) {
-                            const float* side = reinterpret_cast<const float*>(&sm.side[g & 1][wq][0]);
+                            const float* side = reinterpret_cast<const float*>(sm.data + VA_SIDE + ((g & 1) * 4 + wq) * SIDE_BYTES);
                             const bool need = reinterpret_cast<const uint32_t*>(side)[32] != 0;    // warp-uniform
                             if (need) {
                                 // every earlier PV MMA has finished before O is touched
-                                wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 108);
+                                WAIT_WARP_OR_LEAVE(wt, false, &sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 108);
                                 tc_fence_after();
                                 const float f = side[lane];
 #pragma unroll 1
@@ -1134,11 +1120,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         // their probabilities are zero, so their V rows are zeroed to keep 0 * NaN out of O.
                         const int blk = w.blk_begin + 2 * i + h;
                         const int nvalid = w.seqlen - blk * PAGE;
-                        if (MODE == MODE_DENSE && blk < w.blk_end && nvalid < PAGE) {
+                        if (DENSE && blk < w.blk_end && nvalid < PAGE) {
                             const int first = max(nvalid, 0);
                             for (int nh = 0; nh < 2; ++nh) {
                                 const uint32_t slot = (vs + nh) % NVS;
-                                wt.wait<false>(&sm.kv_full[slot], ((vs + nh) / NVS) & 1, 109);
+                                WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_full[slot], ((vs + nh) / NVS) & 1, 109);
                                 uint8_t* vst = sm.data + VA_VRING + slot * V_SLOT_BYTES;
                                 const int nz = (PAGE - first) * 4 * 8;              // rows x boxes x 16-byte chunks
                                 for (int k = threadIdx.x - 128; k < nz; k += 128) {
@@ -1155,16 +1141,14 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 }
                 // ---- epilogue -----------------------------------------------------------------------------------
                 const bool has_tiles = w.ntiles > 0;
-                if (has_tiles) wt.wait<false>(&sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 110);
-                if (threadIdx.x == 128) SPAN(3, nreq);
-                wt.wait<true>(&sm.fin_full, nreq & 1, 111);
-                if (threadIdx.x == 128) SPAN(4, nreq);
+                if (has_tiles) WAIT_WARP_OR_LEAVE(wt, false, &sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 110);
+                WAIT_WARP_OR_LEAVE(wt, true, &sm.fin_full, nreq & 1, 111);
                 tc_fence_after();
-                const float L = sm.fin_l[r], M = sm.fin_m[r];
-                const bool empty = !(L > 0.f) || !has_tiles;          // also catches NaN
-                float scale = empty ? 0.f : 1.f / L;
-                if (MODE != MODE_DENSE && !w.is_split && p.attn_sink && !empty && row_ok)
-                    scale = 1.f / (L + exp2f(p.attn_sink[hd] * kLog2e - M));
+                const float Lsum = fin[r], M = fin[ROWS + r];
+                const bool empty = !(Lsum > 0.f) || !has_tiles;          // also catches NaN
+                float scale = empty ? 0.f : 1.f / Lsum;
+                if (!DENSE && !w.is_split && p.attn_sink && !empty && row_ok)
+                    scale = 1.f / (Lsum + exp2f(p.attn_sink[hd] * kLog2e - M));
                 if (!w.is_split) {
                     __nv_bfloat16* orow = MODE == MODE_PREFILL
                         ? p.out + ((int64_t)w.req * p.h_q + hd) * D_V
@@ -1177,7 +1161,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             uint32_t o[16];
 #pragma unroll
                             for (int e = 0; e < 16; ++e)
-                                o[e] = empty ? 0u : pack_bf16(__uint_as_float(v[2 * e]) * scale, __uint_as_float(v[2 * e + 1]) * scale);
+                                o[e] = empty ? 0u : pack16<FP16>(__uint_as_float(v[2 * e]) * scale, __uint_as_float(v[2 * e + 1]) * scale);
                             if (wide_out) {                   // whole 32-byte sectors per store
                                 st_global_v8(orow + c * 32, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
                                 st_global_v8(orow + c * 32 + 16, o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]);
@@ -1189,10 +1173,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         }
                     }
                     if (row_ok) {
-                        const float lse_nat = empty ? INFINITY : (log2f(L) + M) * kLn2;
+                        const float lse_nat = empty ? INFINITY : (log2f(Lsum) + M) * kLn2;
                         if (MODE == MODE_PREFILL) {
                             p.lse[(int64_t)w.req * p.h_q + hd] = lse_nat;
-                            p.max_logits[(int64_t)w.req * p.h_q + hd] = empty ? -INFINITY : sm.fin_mt[r] * kLn2;
+                            p.max_logits[(int64_t)w.req * p.h_q + hd] = empty ? -INFINITY : fin[2 * ROWS + r] * kLn2;
                         } else {
                             p.lse[w.req * p.l_sb + t * p.l_ss + hd * p.l_sh] = lse_nat;
                         }
@@ -1216,11 +1200,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             }
                         }
                     }
-                    if (row_ok) p.lse_accum[arow] = empty ? -INFINITY : log2f(L) + M;
+                    if (row_ok) p.lse_accum[arow] = empty ? -INFINITY : log2f(Lsum) + M;
                 }
                 tc_fence_before();
-                if (threadIdx.x == 128) SPAN(5, nreq);
-                mbar_arrive_remote(remote_fin_empty);        // fin_l / fin_m may be rewritten
+                mbar_arrive_remote(remote_fin_empty);        // the final statistics may be rewritten
             }
         } else if (MODE == MODE_SPARSE_DECODE) {
             // ---------------- value CTA, FP8 decode: warps 8-11 de-quantise the V slots in place ------------------
@@ -1229,7 +1212,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             const int trow = r & 63, hb = r >> 6, sw = trow & 7;
             const int tq = blockIdx.y;
             uint32_t ks = 0;
-            WaiterT wt_fast(p.status, &sm.aborted);               // this sits on the MMA warp's critical path: no sleeping
+            WaiterT wt_fast(p.status, &sm.aborted, peer_flag, p.wait_limit);   // this sits on the MMA warp's critical path: no sleeping
             for (WalkerT wk(p, part); wk.valid(); wk.next()) {
                 const Work w = wk.get();
                 const int* idx0 = p.sidx[0] + (int64_t)w.req * p.sidx_sb[0] + (int64_t)tq * p.sidx_ss[0];
@@ -1260,7 +1243,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #pragma unroll 1
                         for (int nh = 0; nh < 2; ++nh, ++ks) {
                             const uint32_t slot = ks % NVS;
-                            wt_fast.wait<false>(&sm.raw_full[slot], (ks / NVS) & 1, 206);
+                            WAIT_WARP_OR_LEAVE(wt_fast, false, &sm.raw_full[slot], (ks / NVS) & 1, 206);
                             const float scale = hb ? (nh ? sc.w : sc.y) : (nh ? sc.z : sc.x);
 #pragma unroll 1
                             for (int cj = 0; cj < 2; ++cj) {
@@ -1285,17 +1268,56 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         }
     }
 
+wind_down:
     // ---- wind down: both CTAs leave together, tensor memory is released -----------------------------------
+    if (!DENSE && warp >= 12) cp_async_wait_all();          // this thread's own row copies have landed
     tc_fence_before();
-    __syncthreads();
-    if (threadIdx.x == 0) SPAN(6 + cta_rank, 0);
-    if (sm.aborted) {
-        // a bounded wait ran out somewhere: give copies that may still be in flight time to land
+    if (__syncthreads_or((int)*reinterpret_cast<volatile uint32_t*>(&sm.aborted))) {
+        // A bounded wait ran out in this CTA or in its peer; every thread of this CTA has left its role and issues
+        // nothing more.  Wait - bounded again - for what this CTA still has in flight: its MMAs (they read shared memory
+        // and write tensor memory) and the TMA loads into its rings.
+        if (warp == 1 && lane == 0) {
+            tc_commit(smem_addr(&sm.drain));
+            mbar_wait_bounded<false, 0>(smem_addr(&sm.drain), 0, DRAIN_LIMIT);
+        }
+        if (threadIdx.x == 0) {
+            if (DENSE) {
+                const uint32_t nslots = cta_rank == 0 ? (uint32_t)NKS : (uint32_t)NVS;
+                for (uint32_t back = 1; back <= nslots && back <= fills_armed; ++back) {
+                    const uint32_t f = fills_armed - back;     // one of the last fills this thread armed: its slot has seen no later phase
+                    mbar_wait_bounded<false, 0>(smem_addr(&sm.kv_full[f % nslots]), (f / nslots) & 1, DRAIN_LIMIT);
+                }
+            }
+            if (q_armed) mbar_wait_bounded<false, 0>(smem_addr(&sm.q_landed), (q_armed - 1) & 1, DRAIN_LIMIT);
+        }
+    }
+    cluster_sync();                                            // from here on neither CTA starts anything
+    if (__syncthreads_or((int)*reinterpret_cast<volatile uint32_t*>(&sm.aborted))) {
+        // copies from the peer's shared memory into this one (P pages, final statistics) that were still under way
         const long long t0 = clock64();
-        while (clock64() - t0 < 4000000LL) { }
+        while (clock64() - t0 < SETTLE_CYCLES) { }
     }
     cluster_sync();
     if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---- self-test of the bounded wait: one CTA, one barrier nobody arrives on ---------------------------------
+// Uses the same Waiter and the same reporting as the attention kernels, with nothing in flight (no TMA, no MMA, no
+// cluster): the wait runs into `limit_cycles`, the status words are written, the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles, int code, int* flag_out) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t flag;
+    if (threadIdx.x == 0) { mbar_init(smem_addr(&bar), 1); flag = 0; fence_mbar_init(); }
+    __syncthreads();
+    Waiter<true> lean(status, &flag, 0u, limit_cycles);
+    Waiter<false> spin(status, &flag, 0u, limit_cycles);
+    bool ok = true;
+    if (threadIdx.x < 32) ok = lean.wait<false>(&bar, 0, code);
+    else ok = spin.wait<false>(&bar, 0, code);
+    // a second wait by the same thread returns at once
+    if (threadIdx.x < 32) ok = lean.wait<false>(&bar, 0, code + 1) || ok;
+    __syncthreads();
+    if (threadIdx.x == 0 && flag_out) { flag_out[0] = (int)flag; flag_out[1] = ok ? 1 : 0; }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -1314,19 +1336,39 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+// Barrier-wait limit in SM cycles: the default, or MLA_WAIT_LIMIT_CYCLES from the environment (read once).
+static long long wait_limit_cycles() {
+    static const long long v = [] {
+        const char* e = getenv("MLA_WAIT_LIMIT_CYCLES");
+        const long long x = e ? atoll(e) : 0;
+        return x > 0 ? x : WAIT_LIMIT_DEFAULT;
+    }();
+    return v;
+}
+
+// cudaFuncSetAttribute(max dynamic shared memory) once per kernel instance and device
+template <typename K>
+static int configure_once(K kernel, bool (&done)[64]) {
+    static std::mutex mu;
+    int dev = 0;
+    MLA_CHECK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !done[dev]) {
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        if (dev >= 0 && dev < 64) done[dev] = true;
+    }
+    return MLA_OK;
+}
+
 }  // namespace sm100
 
-#ifdef MLA_TRACE
-extern "C" int mla_debug_trace_copy(void* host_dst) {
-    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_trace, sizeof(sm100::g_trace));
+int launch_bounded_wait_selftest(long long limit_cycles, int code, int* status, int* flag_out, void* stream) {
+    MLA_CHECK_ARG(limit_cycles > 0 && limit_cycles <= 2000000000LL, "mla_selftest_bounded_wait: limit_cycles must be in (0, 2e9]");
+    MLA_CHECK_ARG(status != nullptr, "mla_selftest_bounded_wait: status must not be null");
+    sm100::bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, limit_cycles, code, flag_out);
+    MLA_CHECK_CUDA(cudaGetLastError());
+    return MLA_OK;
 }
-extern "C" int mla_debug_gtrace_copy(void* host_dst) {
-    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_gtrace, sizeof(sm100::g_gtrace));
-}
-extern "C" int mla_debug_span_copy(void* host_dst) {
-    return (int)cudaMemcpyFromSymbol(host_dst, sm100::g_span, sizeof(sm100::g_span));
-}
-#endif
 
 bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
     if (a.d_qk != 576 || a.d_v != 512 || a.page_block_size != 64) return false;
@@ -1347,10 +1389,10 @@ bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
 }
 
 // Tensor map over Q as (576 columns, heads, query tokens, requests) with boxes of 64 columns x box_h heads x box_t
-// tokens, for the first request of every partition.  Returns false (the kernels then load every Q with their own
-// threads) when Q's base or strides do not meet TMA's 16-byte rules or the driver rejects the map.
+// tokens.  Returns false (the kernels then load every Q with their own threads) when Q's base or strides do not meet
+// TMA's 16-byte rules or the driver rejects the map.
 static bool encode_q_map(CUtensorMap* qmap, const void* q, int b, int s_q, int h_q, int64_t sb, int64_t ss, int64_t sh,
-                         int box_h, int box_t, int* box_bytes) {
+                         int box_h, int box_t, int* box_bytes, bool fp16 = false) {
     using namespace sm100;
     static const bool enabled = [] { const char* e = getenv("MLA_Q_TMA"); return !(e && e[0] == '0'); }();
     EncodeTiledFn encode = get_encode_fn();
@@ -1365,18 +1407,28 @@ static bool encode_q_map(CUtensorMap* qmap, const void* q, int b, int s_q, int h
     cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
     cuuint32_t box[4] = {64, (cuuint32_t)box_h, (cuuint32_t)box_t, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = encode(qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = encode(qmap, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q),
+                              dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return false;
     *box_bytes = 128 * box_h * box_t;
     return true;
 }
 
+// The two cache tensor maps of a dense launch depend only on the cache tensor (pointer, strides, pages, heads, type):
+// a decode loop calls with the same cache every step, so the last encoding is kept per host thread.
+struct CacheMaps {
+    const void* k_cache = nullptr;
+    int64_t sb = 0, sr = 0, sh = 0;
+    int num_blocks = 0, h_kv = 0, fp16 = 0;
+    CUtensorMap kmap, vmap;
+};
+
 int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     using namespace sm100;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const bool fp16 = a.dtype == MLA_DTYPE_FP16;
 
     // The cache as a 5-D tensor (64 columns of a chunk, 8 tokens, chunks, 8 token groups, pages): one box brings
     // all 64 tokens of a page for 3 (K) or 4 (V) chunks in a single instruction, and lands as
@@ -1384,30 +1436,39 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     // 3 or 4 KiB between token groups.  (The per-instruction cost of TMA is what limits one SM's fill rate: 8 KiB
     // boxes stream at 35-45 GB/s per SM, 24 KiB boxes at about 90.)
     const int head_chunks = a.h_kv > 1 ? (int)(a.k_stride_head / 64) : 9;
-    CUtensorMap kmap, vmap;
-    cuuint64_t dims[5] = {64, 8, (cuuint64_t)((a.h_kv - 1) * head_chunks + 9), 8, (cuuint64_t)a.num_blocks};
-    cuuint64_t strides[4] = {(cuuint64_t)a.k_stride_row * 2, 128, (cuuint64_t)a.k_stride_row * 16, (cuuint64_t)a.k_stride_block * 2};
-    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    cuuint32_t kbox[5] = {64, 8, 3, 8, 1};
-    cuuint32_t vbox[5] = {64, 8, 4, 8, 1};
-    CUresult r = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(a.k_cache), dims, strides, kbox, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r == CUDA_SUCCESS)
-        r = encode(&vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(a.k_cache), dims, strides, vbox, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    static thread_local CacheMaps cm;
+    if (cm.k_cache != a.k_cache || cm.sb != a.k_stride_block || cm.sr != a.k_stride_row || cm.sh != a.k_stride_head ||
+        cm.num_blocks != a.num_blocks || cm.h_kv != a.h_kv || cm.fp16 != (int)fp16) {
+        cm.k_cache = nullptr;
+        const CUtensorMapDataType dt = fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+        cuuint64_t dims[5] = {64, 8, (cuuint64_t)((a.h_kv - 1) * head_chunks + 9), 8, (cuuint64_t)a.num_blocks};
+        cuuint64_t strides[4] = {(cuuint64_t)a.k_stride_row * 2, 128, (cuuint64_t)a.k_stride_row * 16, (cuuint64_t)a.k_stride_block * 2};
+        cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+        cuuint32_t kbox[5] = {64, 8, 3, 8, 1};
+        cuuint32_t vbox[5] = {64, 8, 4, 8, 1};
+        CUresult r = encode(&cm.kmap, dt, 5, const_cast<void*>(a.k_cache), dims, strides, kbox, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS)
+            r = encode(&cm.vmap, dt, 5, const_cast<void*>(a.k_cache), dims, strides, vbox, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return set_error(MLA_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+        cm.k_cache = a.k_cache; cm.sb = a.k_stride_block; cm.sr = a.k_stride_row; cm.sh = a.k_stride_head;
+        cm.num_blocks = a.num_blocks; cm.h_kv = a.h_kv; cm.fp16 = (int)fp16;
+    }
 
     Params p = {};
     p.b = a.b; p.s_q = a.s_q; p.h_q = a.h_q; p.h_kv = a.h_kv; p.g = a.h_q / a.h_kv;
     p.rows = a.s_q * p.g;
     p.causal = (a.is_causal && a.s_q > 1) ? 1 : 0;
     p.scale_log2 = a.softmax_scale * kLog2e;
+    p.wait_limit = wait_limit_cycles();
     p.q = (const __nv_bfloat16*)a.q; p.q_sb = a.q_stride_b; p.q_ss = a.q_stride_s; p.q_sh = a.q_stride_h;
     p.out = (__nv_bfloat16*)a.out; p.o_sb = a.o_stride_b; p.o_ss = a.o_stride_s; p.o_sh = a.o_stride_h;
     p.lse = a.lse; p.l_sb = a.lse_stride_b; p.l_ss = a.lse_stride_s; p.l_sh = a.lse_stride_h;
     p.block_table = a.block_table; p.bt_sb = a.block_table_stride_b; p.seqlens = a.seqlens_k;
+    p.max_blocks = a.max_blocks_per_seq;
     p.meta = a.meta; p.num_splits = a.num_splits; p.lse_accum = a.lse_accum; p.o_accum = a.o_accum;
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
@@ -1417,17 +1478,18 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     memset(&qmap, 0, sizeof(qmap));
     if (p.row_blocks == 1 || ROWS % p.g == 0)
         p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h, p.g,
-                               p.row_blocks == 1 ? a.s_q : ROWS / p.g, &p.q_box_bytes) ? 1 : 0;
+                               p.row_blocks == 1 ? a.s_q : ROWS / p.g, &p.q_box_bytes, fp16) ? 1 : 0;
 
-    static bool configured[64] = {};
-    int dev = 0;
-    MLA_CHECK_CUDA(cudaGetDevice(&dev));
-    if (dev >= 64 || !configured[dev]) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        if (dev < 64) configured[dev] = true;
-    }
     dim3 grid(2, p.row_blocks * a.h_kv, a.num_sm_parts);
-    attn_sm100_kernel<MODE_DENSE><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, vmap, qmap, p);
+    if (fp16) {
+        static bool configured[64] = {};
+        if (int rc = configure_once(attn_sm100_kernel<MODE_DENSE, true>, configured)) return rc;
+        attn_sm100_kernel<MODE_DENSE, true><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(cm.kmap, cm.vmap, qmap, p);
+    } else {
+        static bool configured[64] = {};
+        if (int rc = configure_once(attn_sm100_kernel<MODE_DENSE, false>, configured)) return rc;
+        attn_sm100_kernel<MODE_DENSE, false><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(cm.kmap, cm.vmap, qmap, p);
+    }
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1449,6 +1511,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     p.b = a.s_q; p.s_q = 1; p.h_q = a.h_q; p.h_kv = 1; p.g = a.h_q; p.rows = a.h_q;
     p.causal = 0;
     p.scale_log2 = a.sm_scale * kLog2e;
+    p.wait_limit = wait_limit_cycles();
     p.q = (const __nv_bfloat16*)a.q; p.q_ss = a.q_stride_s; p.q_sh = a.q_stride_h;
     p.out = (__nv_bfloat16*)a.out; p.lse = a.lse; p.max_logits = a.max_logits;
     p.attn_sink = a.attn_sink;
@@ -1457,14 +1520,9 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
 
-    int dev = 0;
-    MLA_CHECK_CUDA(cudaGetDevice(&dev));
     static bool configured[64] = {};
-    if (dev >= 64 || !configured[dev]) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_PREFILL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        if (dev < 64) configured[dev] = true;
-    }
-    const int sms = device_num_sms(dev);
+    if (int rc = configure_once(attn_sm100_kernel<MODE_PREFILL, false>, configured)) return rc;
+    const int sms = current_device_num_sms();
     int pairs = sms / 2 / p.row_blocks;
     if (pairs < 1) pairs = 1;
     if (pairs > a.s_q) pairs = a.s_q;
@@ -1473,7 +1531,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, 1, a.s_q, a.h_q, 0, a.q_stride_s, a.q_stride_h, a.h_q < ROWS ? a.h_q : ROWS, 1,
                            &p.q_box_bytes) ? 1 : 0;
-    attn_sm100_kernel<MODE_PREFILL><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, qmap, p);
+    attn_sm100_kernel<MODE_PREFILL, false><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, qmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1492,6 +1550,7 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     p.b = a.b; p.s_q = a.s_q; p.h_q = a.h_q; p.h_kv = 1; p.g = a.h_q; p.rows = a.h_q;
     p.causal = 0;
     p.scale_log2 = a.sm_scale * kLog2e;
+    p.wait_limit = wait_limit_cycles();
     p.q = (const __nv_bfloat16*)a.q; p.q_sb = a.q_stride_b; p.q_ss = a.q_stride_s; p.q_sh = a.q_stride_h;
     p.out = (__nv_bfloat16*)a.out; p.o_sb = a.o_stride_b; p.o_ss = a.o_stride_s; p.o_sh = a.o_stride_h;
     p.lse = a.lse; p.l_sb = a.lse_stride_b; p.l_ss = a.lse_stride_s; p.l_sh = a.lse_stride_h;
@@ -1507,20 +1566,15 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     p.sidx[1] = a.extra_indices; p.sidx_sb[1] = a.extra_indices_stride_b; p.sidx_ss[1] = a.extra_indices_stride_s;
     p.stopk[1] = a.extra_kv ? a.extra_topk : 0; p.stopk_len[1] = a.extra_topk_length;
 
-    int dev = 0;
-    MLA_CHECK_CUDA(cudaGetDevice(&dev));
     static bool configured[64] = {};
-    if (dev >= 64 || !configured[dev]) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_sm100_kernel<MODE_SPARSE_DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
-        if (dev < 64) configured[dev] = true;
-    }
+    if (int rc = configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, configured)) return rc;
     CUtensorMap unused_map, qmap;
     memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers K and V with its own threads
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h,
                            a.h_q < ROWS ? a.h_q : ROWS, 1, &p.q_box_bytes) ? 1 : 0;
     dim3 grid(2, a.s_q, a.num_sm_parts);
-    attn_sm100_kernel<MODE_SPARSE_DECODE><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, qmap, p);
+    attn_sm100_kernel<MODE_SPARSE_DECODE, false><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, qmap, p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

@@ -65,7 +65,7 @@ extern "C" {
 
 const char* mla_last_error(void) { return last_error_buffer(); }
 
-int mla_abi_version(void) { return 1; }
+int mla_abi_version(void) { return 2; }
 
 int mla_num_sm_parts(int device, int mode, int h_q, int h_kv, int s_q) {
     const int sms = device_num_sms(device);
@@ -99,14 +99,14 @@ int mla_num_sm_parts_uniform(int device, int mode, int h_q, int h_kv, int s_q, i
         return -1;
     }
     if (b > p) return p;
-    // Every request costs the same, so the greedy scheduler cuts a multiple of b partitions exactly at request
-    // boundaries: no partition then walks two requests (one Q load and one epilogue each instead of two) and, with
-    // one partition per request, nothing is left to combine.  That leaves p - k*b CTA pairs idle; take it when the
-    // extra blocks per partition cost less than the boundary they save (about 8 blocks of 64 tokens, measured).
-    const int k = p / b;
-    const double blocks_even = (double)blocks_per_request / k;
+    // Every request costs the same, so with exactly b partitions the greedy scheduler cuts at every request boundary
+    // (budget = blocks + 2 * overhead per partition, a request costs blocks + overhead: one fits, two do not): no
+    // partition walks two requests (one Q load and one epilogue each instead of two), no request is split and nothing
+    // is left to combine.  That leaves p - b CTA pairs idle; take it when the extra blocks per partition cost less
+    // than the boundary they save (about 8 blocks of 64 tokens, measured).  (For a multiple k > 1 of b the cuts
+    // drift off the request boundaries - the scheduler's budget rounds up - so only k = 1 is offered.)
     const double blocks_greedy = (double)blocks_per_request * b / p;
-    return (blocks_even - blocks_greedy) < 8.0 ? k * b : p;
+    return ((double)blocks_per_request - blocks_greedy) < 8.0 ? b : p;
 }
 
 int mla_get_sched_meta(const mla_sched_meta_args_t* a) {
@@ -127,6 +127,8 @@ int mla_dense_decode_fwd(const mla_dense_decode_args_t* a) {
     if (rc) return rc;
     MLA_CHECK_ARG(a->h_kv > 0 && a->h_q % a->h_kv == 0, "mla_dense_decode_fwd: h_kv (%d) must divide h_q (%d)", a->h_kv, a->h_q);
     MLA_CHECK_ARG(a->page_block_size == 64, "mla_dense_decode_fwd: page_block_size must be 64 (got %d)", a->page_block_size);
+    MLA_CHECK_ARG(a->dtype == MLA_DTYPE_BF16 || a->dtype == MLA_DTYPE_FP16, "mla_dense_decode_fwd: dtype must be MLA_DTYPE_BF16 or MLA_DTYPE_FP16 (got %d)", a->dtype);
+    MLA_CHECK_ARG(a->max_blocks_per_seq > 0, "mla_dense_decode_fwd: max_blocks_per_seq must be positive (got %d)", a->max_blocks_per_seq);
     MLA_CHECK_ARG(a->k_cache && a->block_table && a->seqlens_k, "mla_dense_decode_fwd: k_cache, block_table and seqlens_k must not be null");
     MLA_CHECK_ARG(a->num_blocks > 0, "mla_dense_decode_fwd: num_blocks must be positive");
     MLA_CHECK_ARG(is_aligned16(a->k_cache) && a->k_stride_block % 8 == 0 && a->k_stride_row % 8 == 0 && a->k_stride_head % 8 == 0,
@@ -137,6 +139,8 @@ int mla_dense_decode_fwd(const mla_dense_decode_args_t* a) {
         return launch_dense_decode_sm100(*a);
     }
     if (a->impl == 0 && dense_decode_sm100_supports(*a)) return launch_dense_decode_sm100(*a);
+    if (a->dtype != MLA_DTYPE_BF16)
+        return set_error(MLA_ERR_UNSUPPORTED, "mla_dense_decode_fwd: fp16 is served by the tcgen05 kernel only, which does not support this shape");
     return launch_dense_decode_portable(*a);
 }
 
@@ -189,6 +193,21 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* a) {
     }
     if (a->impl == 0 && sparse_prefill_sm100_supports(*a)) return launch_sparse_prefill_sm100(*a);
     return launch_sparse_prefill_portable(*a);
+}
+
+size_t mla_workspace_bytes(int b, int s_q, int h_q, int d_v, int num_sm_parts, size_t* lse_accum_offset_bytes) {
+    if (b <= 0 || s_q <= 0 || h_q <= 0 || d_v <= 0 || num_sm_parts <= 0) {
+        set_error(MLA_ERR_INVALID_ARG, "mla_workspace_bytes: b, s_q, h_q, d_v and num_sm_parts must be positive");
+        return 0;
+    }
+    const size_t rows = (size_t)(b + num_sm_parts) * (size_t)s_q * (size_t)h_q;
+    const size_t o_bytes = (rows * (size_t)d_v * sizeof(float) + 255) / 256 * 256;
+    if (lse_accum_offset_bytes) *lse_accum_offset_bytes = o_bytes;
+    return o_bytes + rows * sizeof(float);
+}
+
+int mla_selftest_bounded_wait(long long limit_cycles, int code, int32_t* status, int32_t* flag_out, void* stream) {
+    return launch_bounded_wait_selftest(limit_cycles, code, status, flag_out, stream);
 }
 
 int mla_quantize_fp8_kvcache(const mla_quantize_args_t* a) {

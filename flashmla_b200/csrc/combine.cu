@@ -10,6 +10,7 @@
 // fully coalesced 512 B per warp instruction), split weights are computed once per 32 splits and
 // broadcast by shuffle, so there is no limit on the number of splits.
 #include "common.cuh"
+#include <cuda_fp16.h>
 
 namespace mla {
 
@@ -65,14 +66,22 @@ combine_kernel(const mla_combine_args_t a) {
             }
         }
     }
+    // out is bf16 or fp16: both are 2 bytes wide
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + req * a.o_stride_b + t * a.o_stride_s + head * a.o_stride_h;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
-        __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
         uint2 packed;
-        packed.x = *reinterpret_cast<uint32_t*>(&lo);
-        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        if (a.dtype == MLA_DTYPE_FP16) {
+            __half2 lo = __floats2half2_rn(acc[i].x, acc[i].y);
+            __half2 hi = __floats2half2_rn(acc[i].z, acc[i].w);
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
+            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        }
         *reinterpret_cast<uint2*>(o + (lane + i * 32) * 4) = packed;
     }
 }
@@ -80,6 +89,7 @@ combine_kernel(const mla_combine_args_t a) {
 int launch_combine(const mla_combine_args_t& a) {
     MLA_CHECK_ARG(a.b > 0 && a.s_q > 0 && a.h_q > 0, "combine: b, s_q, h_q must be positive");
     MLA_CHECK_ARG(a.d_v == 512, "combine: only d_v == 512 is supported (got %d)", a.d_v);
+    MLA_CHECK_ARG(a.dtype == MLA_DTYPE_BF16 || a.dtype == MLA_DTYPE_FP16, "combine: dtype must be MLA_DTYPE_BF16 or MLA_DTYPE_FP16 (got %d)", a.dtype);
     MLA_CHECK_ARG(a.lse && a.out && a.lse_accum && a.o_accum && a.num_splits, "combine: null pointer");
     MLA_CHECK_ARG(is_aligned16(a.o_accum), "combine: o_accum must be 16-byte aligned");
     MLA_CHECK_ARG(((uintptr_t)a.out & 7u) == 0 && a.o_stride_b % 4 == 0 && a.o_stride_s % 4 == 0 && a.o_stride_h % 4 == 0,

@@ -49,6 +49,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a);
 bool sparse_decode_sm100_supports(const mla_sparse_decode_args_t& a);
 int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a);
 int launch_quantize_fp8(const mla_quantize_args_t& a);
+int launch_bounded_wait_selftest(long long limit_cycles, int code, int* status, int* flag_out, void* stream);
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;

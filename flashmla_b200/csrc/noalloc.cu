@@ -6,7 +6,7 @@
 // owning a device allocator at all.  For them the split-KV scratch that mla_dense_decode_fwd expects from
 // the caller lives here, in a fixed array inside the library image.
 //
-// Cost and limits: every GPU that loads the library keeps MLA_NOALLOC_MAX_ROWS * 513 floats (about 32 MiB)
+// Cost and limits: every GPU that loads the library keeps MLA_NOALLOC_MAX_ROWS * 513 floats (about 64 MiB)
 // resident until the process exits.  The array is shared by all calls on a device and keeps the previous
 // call's contents; no part of it has to start at zero (each split slot a request uses is written in full
 // before the combine step reads it), so nothing is cleared.  Two calls whose kernels can overlap on the
@@ -15,19 +15,25 @@
 // This entry point has no counterpart in the reference.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace mla {
 
 // rows = (b + num_sm_parts) * s_q * h_q; per row 512 fp32 partial outputs + 1 fp32 base-2 LSE
 static __device__ __align__(256) float g_noalloc_scratch[(size_t)MLA_NOALLOC_MAX_ROWS * 513];
 
 // In host code the array's name is only a handle: the device address has to be asked for, per device, with
-// that device current.  Done on the first call on each device and cached.
+// that device current.  Done on the first call on each device and cached (under a lock: two host threads may
+// make their first call at the same time).  The cache is keyed by device ordinal and is not refreshed after a
+// cudaDeviceReset.
 static float* g_scratch_ptr[64] = {};
+static std::mutex g_scratch_mu;
 
 static int scratch_for_current_device(float** out) {
     int dev = 0;
     MLA_CHECK_CUDA(cudaGetDevice(&dev));
     MLA_CHECK_ARG(dev >= 0 && dev < 64, "mla_dense_decode_noalloc: device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
     if (!g_scratch_ptr[dev]) {
         void* p = nullptr;
         MLA_CHECK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
@@ -65,6 +71,7 @@ extern "C" int mla_dense_decode_noalloc(const mla_dense_decode_args_t* args) {
     c.lse = a.lse; c.lse_stride_b = a.lse_stride_b; c.lse_stride_s = a.lse_stride_s; c.lse_stride_h = a.lse_stride_h;
     c.out = a.out; c.o_stride_b = a.o_stride_b; c.o_stride_s = a.o_stride_s; c.o_stride_h = a.o_stride_h;
     c.lse_accum = a.lse_accum; c.o_accum = a.o_accum; c.num_splits = a.num_splits; c.attn_sink = nullptr;
+    c.dtype = a.dtype;
     c.stream = a.stream;
     return mla_combine(&c);
 }

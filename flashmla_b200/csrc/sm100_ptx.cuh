@@ -190,6 +190,8 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 // Waits until at most N of this thread's committed cp.async groups are still in flight.
 template <int N>
 __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// Waits until every cp.async copy this thread has issued has landed.
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -234,6 +236,17 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_remote(uint32_t cluster_ba
 }
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Named barrier that also ORs a flag over its `nthreads` participants: every one of them gets the same answer.
+__device__ __forceinline__ bool named_bar_red_or(int id, int nthreads, bool flag) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 p, %1, 0;\n\t"
+        "bar.red.or.pred q, %2, %3, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"((uint32_t)flag), "r"(id), "r"(nthreads) : "memory");
+    return r != 0;
 }
 
 // ---- shared-memory stores into the other CTA of the cluster ---------------------------------------------
@@ -287,6 +300,11 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr, uint32_t lbo
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) |
            ((uint32_t)(M >> 4) << 24);
+}
+// The same with the 16-bit input type chosen: bf16 (format code 1 for A and B) or fp16 (format code 0).
+__host__ __device__ constexpr uint32_t make_idesc_16(int M, int N, bool b_mn_major, bool fp16) {
+    return (1u << 4) | ((fp16 ? 0u : 1u) << 7) | ((fp16 ? 0u : 1u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]

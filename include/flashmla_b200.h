@@ -44,6 +44,10 @@ typedef struct {
     int32_t _pad;                   /* never written                                          */
 } mla_sched_meta_t;
 
+/* Element type of q, the KV cache and out (dense decode; everything else is bf16).  Accumulation is fp32 either way. */
+#define MLA_DTYPE_BF16  0
+#define MLA_DTYPE_FP16  1
+
 /* Which decode kernel family the partition count is asked for. */
 #define MLA_MODE_DENSE_DECODE   0
 #define MLA_MODE_SPARSE_DECODE  1
@@ -100,16 +104,16 @@ typedef struct {
     int32_t is_causal;
     float softmax_scale;
 
-    const void* q;                    /* bf16 [b, s_q, h_q, d_qk]                              */
+    const void* q;                    /* bf16 or fp16 (see dtype) [b, s_q, h_q, d_qk]          */
     int64_t q_stride_b, q_stride_s, q_stride_h;
-    const void* k_cache;              /* bf16 [num_blocks, page_block_size, h_kv, d_qk]        */
+    const void* k_cache;              /* same type [num_blocks, page_block_size, h_kv, d_qk]   */
     int64_t k_stride_block, k_stride_row, k_stride_head;
     const int32_t* block_table;       /* [b, max_blocks_per_seq]                               */
     int64_t block_table_stride_b;
     int32_t max_blocks_per_seq;
     const int32_t* seqlens_k;         /* [b]                                                   */
 
-    void* out;                        /* bf16 [b, s_q, h_q, d_v]                               */
+    void* out;                        /* same type as q [b, s_q, h_q, d_v]                     */
     int64_t o_stride_b, o_stride_s, o_stride_h;
     float* lse;                       /* fp32, element (b, s, h) at b*lse_stride_b + s*lse_stride_s + h*lse_stride_h */
     int64_t lse_stride_b, lse_stride_s, lse_stride_h;
@@ -123,6 +127,7 @@ typedef struct {
 
     int32_t* status;                  /* optional device int32[4]; nonzero [0] after the launch means a bounded wait ran out */
     int32_t impl;                     /* 0 = pick the fastest kernel that supports the shape; 1 = portable kernel; 2 = tcgen05 kernel */
+    int32_t dtype;                    /* MLA_DTYPE_BF16 or MLA_DTYPE_FP16 (the reference accepts both: csrc/api/dense_decode.h:33) */
     void* stream;
 } mla_dense_decode_args_t;
 int mla_dense_decode_fwd(const mla_dense_decode_args_t* args);
@@ -183,15 +188,25 @@ typedef struct {
     int32_t b, s_q, h_q, d_v;
     float* lse;
     int64_t lse_stride_b, lse_stride_s, lse_stride_h;
-    void* out;                        /* bf16                                                  */
+    void* out;                        /* bf16 or fp16 (see dtype)                              */
     int64_t o_stride_b, o_stride_s, o_stride_h;
     const float* lse_accum;           /* [splits, s_q, h_q] contiguous                         */
     const float* o_accum;             /* [splits, s_q, h_q, d_v] contiguous                    */
     const int32_t* num_splits;        /* [b + 1]                                               */
     const float* attn_sink;           /* [h_q] or NULL                                         */
+    int32_t dtype;                    /* type of out: MLA_DTYPE_BF16 or MLA_DTYPE_FP16         */
+    int32_t _pad;
     void* stream;
 } mla_combine_args_t;
 int mla_combine(const mla_combine_args_t* args);
+
+/* Size of the split-KV scratch of one decode launch, for callers that allocate it themselves: the two decode entry
+ * points above take o_accum [b + num_sm_parts, s_q, h_q, d_v] and lse_accum [b + num_sm_parts, s_q, h_q], both fp32,
+ * the buffers the reference allocates inside its host glue (csrc/api/dense_decode.h:165-166,
+ * csrc/api/sparse_decode.h:315-316).  Returns the bytes of ONE allocation that holds o_accum at offset 0 and lse_accum
+ * at *lse_accum_offset_bytes (a multiple of 256, so both meet the kernels' alignment rules when the allocation is
+ * 256-byte aligned); returns 0 and sets the error message on bad arguments.  Host-only: touches no device. */
+size_t mla_workspace_bytes(int b, int s_q, int h_q, int d_v, int num_sm_parts, size_t* lse_accum_offset_bytes);
 
 /* Token-sparse MLA prefill forward.  Replaces run_fwd_phase1_kernel as driven by
  * sparse_attn_prefill_interface (csrc/api/sparse_fwd.h:101-243); arguments mirror
@@ -221,13 +236,14 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* args);
  * decode loop runs on a memory plan fixed at start-up, where a cudaMalloc would stall the device or fail;
  * host runtimes that bind this ABI without a device allocator).  Same arguments as mla_dense_decode_fwd, but
  * args->lse_accum and args->o_accum are ignored: the split-KV scratch is a fixed array inside the library,
- * about 32 MiB per GPU that loads it, held until the process exits.  Limit: (b + num_sm_parts) * s_q * h_q
+ * about 64 MiB per GPU that loads it, held until the process exits (enough for batch 128 with 128 heads on a 148-SM part:
+ * (128 + 74) * 128 = 25856 rows).  Limit: (b + num_sm_parts) * s_q * h_q
  * must not exceed MLA_NOALLOC_MAX_ROWS, otherwise MLA_ERR_INVALID_ARG is returned.  The first call on each
  * device looks up the array's device address (make that call with the device current and before any stream
  * capture).  All calls on a GPU share the array: calls that may overlap on the GPU race and must be
  * serialised by the caller.  Nothing in the array needs clearing between calls.  Calls no allocation routine.
  * This entry point has no counterpart in the reference. */
-#define MLA_NOALLOC_MAX_ROWS 16384
+#define MLA_NOALLOC_MAX_ROWS 32768
 int mla_dense_decode_noalloc(const mla_dense_decode_args_t* args);
 
 /* FP8 KV-cache writer (the step before sparse decode): bf16 token rows -> 656-byte records.  Replaces the torch
@@ -247,6 +263,16 @@ typedef struct {
     void* stream;
 } mla_quantize_args_t;
 int mla_quantize_fp8_kvcache(const mla_quantize_args_t* args);
+
+/* Self-test of the kernels' bounded barrier wait: launches one small CTA that waits, with the same helper the
+ * attention kernels use, on a barrier nobody arrives on, with nothing else in flight.  After `limit_cycles` SM
+ * cycles (at most 2e9) every one of its 64 threads gives up, the kernel returns normally and status[0] == code,
+ * status[1] == 64 (status: device int32[4], zeroed by the caller); flag_out (device int32[2], optional) receives
+ * {1, 0}: the CTA's abort flag, and the result of the wait.  This is how an expired wait looks to a caller of the
+ * entry points above, which all take the same `status` words.  The default limit of the attention kernels is 2e9
+ * cycles; the environment variable MLA_WAIT_LIMIT_CYCLES, read once, overrides it.
+ * No counterpart in the reference (its kernels wait without a limit). */
+int mla_selftest_bounded_wait(long long limit_cycles, int code, int32_t* status, int32_t* flag_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -22,7 +22,7 @@ def test_library_exports_every_declared_symbol():
     lib = _capi.lib()
     for name in declared:
         assert hasattr(lib, name), f"{name} not exported"
-    assert lib.mla_abi_version() == 1
+    assert lib.mla_abi_version() == 2
     assert lib.mla_last_error() == b""
 
 
