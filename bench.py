@@ -52,7 +52,7 @@ def reduce_over_ranks(ms_total, ms_e2e_total, units, tokens, flops, nbytes, dist
 
 
 def make_workload(name, device, seed, prefill_sq=4096):
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     if name in ("dense", "dense_sq2"):
         s_q = 2 if name == "dense_sq2" else 1
         b, h_q = 128, 128

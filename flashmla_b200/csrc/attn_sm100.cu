@@ -245,7 +245,9 @@ struct Walker<MODE_PREFILL> {
 
 // What a thread does when one of its bounded waits runs out: first code and a count in the global status words,
 // the `aborted` flag of this CTA and of its peer.  Shared with the self-test kernel at the end of this file.
-__device__ __forceinline__ void report_expired_wait(int* status, uint32_t* flag, uint32_t peer_flag, int code) {
+// (Out of line on purpose: inlined at every wait site it cost the dense kernel 10 % - 0.176 against 0.160 ms - although
+// it never runs: the hot loops of all roles have to share the instruction cache.)
+__device__ __noinline__ void report_expired_wait(int* status, uint32_t* flag, uint32_t peer_flag, int code) {
     *reinterpret_cast<volatile uint32_t*>(flag) = 1;
     if (peer_flag) st_cluster_u32(peer_flag, 1u);
     if (status) { atomicCAS(status, 0, code); atomicAdd(status + 1, 1); }
@@ -282,6 +284,8 @@ struct Waiter {
 // whole warps (all 32 lanes execute this): leave together, tcgen05.ld/st and shuffles are warp-collective
 #define WAIT_WARP_OR_LEAVE(W, CL, bar, par, code) \
     do { (W).template wait<CL>(bar, par, code); if (__any_sync(0xffffffffu, (W).aborted)) goto wind_down; } while (0)
+// the two softmax warpgroups of the score CTA: their named barrier carries the flag
+#define BAR_OR_LEAVE(flag) do { if (named_bar_red_or(1, 256, flag)) goto wind_down; } while (0)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -321,6 +325,63 @@ __device__ __forceinline__ const uint8_t* shfl_ptr(const uint8_t* ptr, int src_l
     const uint32_t lo = __shfl_sync(0xffffffffu, (uint32_t)v, src_lane);
     const uint32_t hi = __shfl_sync(0xffffffffu, (uint32_t)(v >> 32), src_lane);
     return reinterpret_cast<const uint8_t*>(((unsigned long long)hi << 32) | lo);
+}
+
+// Rare paths of the value CTA's correction warpgroup, kept out of line so that the loop around them stays small.
+// O rows times their rescale factor (each thread its own row = tensor-memory lane).
+__device__ __noinline__ void rescale_o_rows(uint32_t tlane, float f) {
+#pragma unroll 1
+    for (int c = 0; c < D_V / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tlane + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * f);
+        tmem_st32(tlane + c * 32, v);
+    }
+    tmem_wait_st();
+}
+// Rows [first, 64) of a dense V slot ([8-token group][chunk][8 rows x 128 B]) set to zero by threads 128..255.
+__device__ __noinline__ void zero_v_rows(uint8_t* vst, int first) {
+    const int nz = (PAGE - first) * 4 * 8;              // rows x boxes x 16-byte chunks
+    for (int k = threadIdx.x - 128; k < nz; k += 128) {
+        const int chunk = k & 7, box = (k >> 3) & 3, rr = first + (k >> 5);
+        *reinterpret_cast<uint4*>(vst + (rr >> 3) * 4096 + box * 1024 + (rr & 7) * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// A request's Q row moved by the softmax threads themselves, one thread per row: the path for Q tensors whose base or
+// strides do not fit a TMA box (several times slower than the boxes; kept out of line, it is rarely taken).
+// Warpgroup `half` takes its share of the chunks: to tensor memory, in the gather modes chunks 7 / 8 to shared memory.
+template <int MODE>
+__device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qrow, bool row_ok, int half, int r, uint32_t tlane) {
+    using L = Lay<MODE>;
+    constexpr bool DENSE = MODE == MODE_DENSE;
+    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT, c_smem = half ? 8 : 7;
+#pragma unroll 1
+    for (int c = c_begin; c < c_end + (DENSE ? 0 : 1); ++c) {
+        const int chunk = c < c_end ? c : c_smem;
+        uint32_t v[32];
+        if (row_ok) {
+            const uint4* src = reinterpret_cast<const uint4*>(qrow + chunk * 64);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint4 x = __ldg(src + i);
+                v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (c < c_end) {
+            tmem_st32(tlane + L::TM_Q + chunk * 32, v);
+        } else {
+            uint8_t* qdst = sm.data + L::SC_Q78 + (chunk - L::Q_TMEM_CHUNKS) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                *reinterpret_cast<uint4*>(qdst + ((ch ^ (r & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+        }
+    }
 }
 
 // FP16: q, the cache and out are fp16 instead of bf16 (dense mode only); accumulation is fp32 either way.
@@ -523,14 +584,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         // The probe of the next group's barrier is issued before this group's MMAs so that its
                         // latency hides behind them (the MMA queue is shallow: time the issuing thread spends
                         // waiting is time the tensor pipe idles).
+                        // (gather modes: three slots, so group j of every tile sits in slot j with the tile's parity and
+                        // every address below is a compile-time offset)
+                        if (!DENSE) { slot = 0; par = g & 1; }
                         bool ready = mbar_try_wait(kv_full0 + slot * 8, par);
 #pragma unroll
                         for (int grp = 0; grp < 3; ++grp) {
-                            if (!ready) WAIT_OR_LEAVE(wt, false, &sm.kv_full[slot], par, 3);
+                            const uint32_t cur = DENSE ? slot : (uint32_t)grp;
+                            if (!ready) WAIT_OR_LEAVE(wt, false, &sm.kv_full[cur], par, 3);
                             tc_fence_after();
-                            const uint32_t cur = slot;
-                            if (++slot == (uint32_t)NKS) { slot = 0; par ^= 1; }
-                            if (grp < 2) ready = mbar_try_wait(kv_full0 + slot * 8, par);
+                            if (DENSE) { if (++slot == (uint32_t)NKS) { slot = 0; par ^= 1; } }
+                            if (grp < 2) ready = mbar_try_wait(kv_full0 + (DENSE ? slot : (uint32_t)(grp + 1)) * 8, par);
                             const uint32_t grp_lo = kring_lo + cur * (K_GROUP_BYTES >> 4);
 #pragma unroll
                             for (int c = 0; c < 3; ++c) {
@@ -916,7 +980,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const __nv_bfloat16* qrow = MODE == MODE_PREFILL
                         ? p.q + (int64_t)w.req * p.q_ss + (int64_t)hd * p.q_sh
                         : p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
-                    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT, c_smem = half ? 8 : 7;
+                    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT;
                     if (p.q_tma) {
                         // Q arrived as TMA boxes: in the gather modes chunks 7 and 8 are in place; the others wait in the K
                         // ring as [row][128 B] with the 128-byte swizzle
@@ -934,30 +998,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         }
                         tmem_wait_st();
                         if (!wt.aborted) mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
-                    } else
-#pragma unroll 1
-                    for (int c = c_begin; c < c_end + (DENSE ? 0 : 1); ++c) {
-                        const int chunk = c < c_end ? c : c_smem;
-                        uint32_t v[32];
-                        if (row_ok) {
-                            const uint4* src = reinterpret_cast<const uint4*>(qrow + chunk * 64);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const uint4 x = __ldg(src + i);
-                                v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = 0u;
-                        }
-                        if (c < c_end) {
-                            tmem_st32(tlane + L::TM_Q + chunk * 32, v);
-                        } else {
-                            uint8_t* qdst = sm.data + L::SC_Q78 + (chunk - L::Q_TMEM_CHUNKS) * 16384 + (r >> 3) * 1024 + (r & 7) * 128;
-#pragma unroll
-                            for (int ch = 0; ch < 8; ++ch)
-                                *reinterpret_cast<uint4*>(qdst + ((ch ^ (r & 7)) << 4)) = make_uint4(v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
-                        }
+                    } else {
+                        load_q_by_threads<MODE>(sm, qrow, row_ok, half, r, tlane);
                     }
                     tmem_wait_st();
                     fence_proxy_async_smem();
@@ -1013,7 +1055,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     float mx = fmaxf(mx0, mx1);
                     // the row maximum over both pages of the tile; the barrier also carries the abort flag
                     xmax[((g & 1) * 2 + half) * ROWS + r] = mx;
-                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
+                    BAR_OR_LEAVE(wt.aborted);
                     mx = fmaxf(mx, xmax[((g & 1) * 2 + (half ^ 1)) * ROWS + r]);
                     mx *= p.scale_log2;                                // scale > 0: max commutes with scaling
                     m_true = fmaxf(m_true, mx);
@@ -1061,9 +1103,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                 {
                     float* lsum = DENSE ? xmax + ((g & 1) * 2) * ROWS : reinterpret_cast<float*>(sm.data + L::SC_LSUM);
                     if (half == 1) lsum[r] = l_run;
-                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
+                    BAR_OR_LEAVE(wt.aborted);
                     if (half == 0) l_run += lsum[r];
-                    if (named_bar_red_or(1, 256, wt.aborted)) goto wind_down;
+                    BAR_OR_LEAVE(wt.aborted);
                 }
                 if (half == 0) {
                     wt.template wait<true>(&sm.fin_empty, (nreq & 1) ^ 1, 7);
@@ -1103,17 +1145,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                                 // every earlier PV MMA has finished before O is touched
                                 WAIT_WARP_OR_LEAVE(wt, false, &sm.pv_done[((g - 1) & 1) * 2 + 1], ((g - 1) >> 1) & 1, 108);
                                 tc_fence_after();
-                                const float f = side[lane];
-#pragma unroll 1
-                                for (int c = 0; c < D_V / 32; ++c) {
-                                    uint32_t v[32];
-                                    tmem_ld32(tlane + c * 32, v);
-                                    tmem_wait_ld();
-#pragma unroll
-                                    for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * f);
-                                    tmem_st32(tlane + c * 32, v);
-                                }
-                                tmem_wait_st();
+                                rescale_o_rows(tlane, side[lane]);
                             }
                         }
                         // Tokens at or beyond the sequence length may hold anything (NaN included) in a real page:
@@ -1125,13 +1157,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             for (int nh = 0; nh < 2; ++nh) {
                                 const uint32_t slot = (vs + nh) % NVS;
                                 WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_full[slot], ((vs + nh) / NVS) & 1, 109);
-                                uint8_t* vst = sm.data + VA_VRING + slot * V_SLOT_BYTES;
-                                const int nz = (PAGE - first) * 4 * 8;              // rows x boxes x 16-byte chunks
-                                for (int k = threadIdx.x - 128; k < nz; k += 128) {
-                                    const int chunk = k & 7, box = (k >> 3) & 3, rr = first + (k >> 5);
-                                    // dense V slot: [8-token group][chunk][8 rows x 128 B]
-                                    *reinterpret_cast<uint4*>(vst + (rr >> 3) * 4096 + box * 1024 + (rr & 7) * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
-                                }
+                                zero_v_rows(sm.data + VA_VRING + slot * V_SLOT_BYTES, first);
                             }
                             fence_proxy_async_smem();
                         }

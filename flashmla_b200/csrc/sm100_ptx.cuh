@@ -120,13 +120,30 @@ __device__ __forceinline__ bool mbar_wait_bounded_parked(uint32_t bar, uint32_t 
 // either way, and the two families want opposite things (measured): the TMA-fed dense kernel is 3.5 % faster without
 // them (they are a third of its code, copied to every wait site), the gather-fed kernels are 25 % slower without them
 // or with the same probes in a rolled loop.
+// The timed loop of a bounded wait, out of line (build option MLA_OUTLINE_TIMED_WAIT; measured 3 % slower for the dense
+// kernel than the inlined loop: a wait that is not served at once is the common case there, and the call costs more
+// than the copy of the loop).
+template <bool CLUSTER_SCOPE>
+__device__ __noinline__ bool mbar_wait_timed(uint32_t bar, uint32_t parity, long long limit_cycles) {
+    const long long t0 = clock64();
+#pragma unroll 1
+    while (true) {
+        if (CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > limit_cycles) return false;
+    }
+}
 template <bool CLUSTER_SCOPE, int PRESPIN = 64>
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit_cycles) {
 #pragma unroll
     for (int i = 0; i < PRESPIN; ++i) {
         if (CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     }
-    if (PRESPIN == 0 && (CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))) return true;
+    if (PRESPIN == 0) {
+        if (CLUSTER_SCOPE ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+#ifdef MLA_OUTLINE_TIMED_WAIT
+        return mbar_wait_timed<CLUSTER_SCOPE>(bar, parity, limit_cycles);
+#endif
+    }
     const long long t0 = clock64();
 #pragma unroll 1
     while (true) {

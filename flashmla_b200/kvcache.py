@@ -2,9 +2,8 @@
 
 Per token 656 bytes: 512 float8_e4m3fn "NoPE" values quantised per group of 128 with one fp32
 scale per group (x ~= fp8 * scale), the 4 scales, then 64 bf16 "RoPE" values stored as they are
-(layout: flash_mla/flash_mla_interface.py:92-98 of the reference).  CUDA tensors are quantised by the
-library's kernel (mla_quantize_fp8_kvcache); CPU tensors, which only tests and fixture generators pass,
-by the torch statement of the same arithmetic below.
+(layout: flash_mla/flash_mla_interface.py:92-98 of the reference).  The records are written by the library's
+kernel (mla_quantize_fp8_kvcache); there is no CPU path.
 """
 import torch
 
@@ -23,52 +22,16 @@ def quantize_fp8_kvcache(blocked_k: torch.Tensor, pow2_scale: bool = False, pad_
     nb, bs, h_k, d = blocked_k.shape
     assert h_k == 1 and d == D_QK
     assert blocked_k.dtype == torch.bfloat16
+    if not blocked_k.is_cuda:
+        raise RuntimeError("blocked_k must be a CUDA tensor (this library has no CPU path)")
     x = blocked_k.squeeze(2)
     buf = torch.empty((nb, bs + pad_rows, BYTES_PER_TOKEN), dtype=torch.float8_e4m3fn, device=blocked_k.device)
     res = buf[:, :bs, :]
-    if blocked_k.is_cuda:
-        assert x.stride(-1) == 1, "the last dimension of blocked_k must be contiguous"
-        with torch.cuda.device(blocked_k.device):
-            args = _capi.QuantizeArgs(
-                x=_capi.ptr(x), x_stride_block=x.stride(0), x_stride_row=x.stride(1), num_blocks=nb, block_size=bs,
-                out=_capi.ptr(buf), out_stride_block_bytes=buf.stride(0), pow2_scale=1 if pow2_scale else 0,
-                stream=torch.cuda.current_stream().cuda_stream)
-            _capi.check(_capi.lib().mla_quantize_fp8_kvcache(args), "mla_quantize_fp8_kvcache")
-        return res.view(nb, bs, 1, BYTES_PER_TOKEN)
-    grp = x[..., :D_NOPE].reshape(nb, bs, NUM_GROUPS, GROUP).float()
-    scale = grp.abs().amax(dim=-1) / 448.0
-    if pow2_scale:
-        scale = torch.pow(2, torch.clamp_min(scale, 1e-4).log2().ceil())
-    else:
-        scale = torch.clamp_min(scale, 1e-30)
-    res[..., :D_NOPE] = (grp / scale.unsqueeze(-1)).reshape(nb, bs, D_NOPE).to(torch.float8_e4m3fn)
-    res[..., D_NOPE:D_NOPE + 4 * NUM_GROUPS].view(torch.float32)[:] = scale
-    res[..., D_NOPE + 4 * NUM_GROUPS:].view(torch.bfloat16)[:] = x[..., D_NOPE:]
+    assert x.stride(-1) == 1, "the last dimension of blocked_k must be contiguous"
+    with torch.cuda.device(blocked_k.device):
+        args = _capi.QuantizeArgs(
+            x=_capi.ptr(x), x_stride_block=x.stride(0), x_stride_row=x.stride(1), num_blocks=nb, block_size=bs,
+            out=_capi.ptr(buf), out_stride_block_bytes=buf.stride(0), pow2_scale=1 if pow2_scale else 0,
+            stream=torch.cuda.current_stream().cuda_stream)
+        _capi.check(_capi.lib().mla_quantize_fp8_kvcache(args), "mla_quantize_fp8_kvcache")
     return res.view(nb, bs, 1, BYTES_PER_TOKEN)
-
-
-if __name__ == "__main__":
-    # python -m flashmla_b200.kvcache [--blocks N]: times the cache-write kernel on N blocks of 64 random bf16 rows
-    import argparse
-    import json
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--blocks", type=int, default=32768)
-    ap.add_argument("--steps", type=int, default=10)
-    a = ap.parse_args()
-    if not torch.cuda.is_available():
-        raise SystemExit("needs a CUDA device (there is no CPU path)")
-    x = torch.randn(a.blocks, 64, 1, D_QK, device="cuda", dtype=torch.bfloat16)
-    for _ in range(3):
-        quantize_fp8_kvcache(x)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(a.steps):
-        quantize_fp8_kvcache(x)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / a.steps
-    ntok = a.blocks * 64
-    print(json.dumps({"kernel": "quantize_fp8_kernel", "tokens": ntok, "ms": ms,
-                      "gbs": ntok * (2 * D_QK + BYTES_PER_TOKEN) / ms / 1e6, "bytes_per_token": 2 * D_QK + BYTES_PER_TOKEN}))

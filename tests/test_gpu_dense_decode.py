@@ -37,7 +37,7 @@ def test_golden_fixtures(golden_dir):
 
 
 def _case(b, s_q, h_q, h_kv, seqlens, causal, seed, noncontig=False, impl=0):
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     seq = torch.tensor(seqlens, dtype=torch.int32)
     d = W.dense_decode_inputs(seq, s_q, h_q, h_kv, seed=seed, device="cpu", poison_unused=True)
     ref_out, ref_lse = attention.dense_decode(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], 512, causal)
@@ -84,7 +84,7 @@ def test_many_splits_long_sequence():
 def test_serving_shape_sample():
     """Serving shape (batch 128, h_q 128, seqlens ~ N(4096, 512^2) clipped to [1, 8192], one forced to 8192,
     causal, s_q in {1, 2}): the full batch runs on the GPU, a sample of requests is checked against the oracle."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     import flashmla_b200 as fm
     seq = W.seqlens_normal(128, 4096, 512, 1, 8192, True, seed=0)
     for s_q in (1, 2):
@@ -109,7 +109,7 @@ def test_longcontext_shard_sample():
     """Long-context sweep (1024 requests, log-normal lengths with median 8192, sigma 1, clipped to [256, 131072]):
     the shard that one of eight GPUs gets (128 requests) runs in full; the longest, the shortest and three other
     requests are checked against the oracle on their own pages, the whole shard through size-independent properties."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     import flashmla_b200 as fm
     seq_all = W.seqlens_lognormal(1024, 8192, 1.0, 256, 131072, seed=0)
     seq = seq_all[3 * 128:4 * 128].contiguous()

@@ -56,7 +56,7 @@ def test_sparse_decode_golden(golden_dir):
     (2, 3, 16, 640, 192, False, False),
 ])
 def test_sparse_decode_cases(b, s_q, h_q, s_kv, topk, pow2, sink):
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_decode_inputs(b, s_q, h_q, s_kv, topk, seed=b * 10 + s_q, device="cpu", pow2_scale=pow2, pad_rows=1)
     assert d["kv_fp8"].stride(0) == 65 * 656
     kv_deq = quant.dequantize_v32(d["kv_fp8"])
@@ -77,7 +77,7 @@ def test_sparse_decode_cases(b, s_q, h_q, s_kv, topk, pow2, sink):
 def test_sparse_decode_all_invalid_and_unused_nan():
     """A request whose indices are all -1 gives out = 0 and lse = +inf; cache rows that no index refers to may
     hold NaN bytes without leaking into the result."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_decode_inputs(3, 1, 128, 512, 128, seed=3, device="cpu")
     d["indices"][1] = -1
     kv = d["kv_fp8"].clone()
@@ -96,7 +96,7 @@ def test_sparse_decode_all_invalid_and_unused_nan():
 def test_sparse_decode_config3_sample():
     """batch 64, h_q 128, 32768 tokens per sequence, topk 2048 with the last 5% of each row -1, scale = amax/448:
     the whole batch runs on the GPU, a sample of requests is checked against the oracle."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_decode_inputs(64, 1, 128, 32768, 2048, seed=0, device=DEV, data_on_device=True)
     out, lse = _decode(d["q"], d["kv_fp8"], d["indices"], 576 ** -0.5)
     sample = [0, 31, 63]
@@ -142,7 +142,7 @@ def test_sparse_prefill_golden_both_kernel_families(golden_dir, impl):
 
 @pytest.mark.parametrize("s_q,h_q,s_kv,topk", [(62, 128, 2000, 256), (7, 64, 300, 128), (33, 128, 128, 384)])
 def test_sparse_prefill_cases(s_q, h_q, s_kv, topk):
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_prefill_inputs(s_q, h_q, s_kv, topk, seed=s_q, device="cpu")
     zoo = torch.tensor([-2147483648, -123456, -1, s_kv, 114514, 1919810, 2147480000, 2147483647], dtype=torch.int32)
     idx = d["indices"]
@@ -159,7 +159,7 @@ def test_sparse_prefill_cases(s_q, h_q, s_kv, topk):
 def test_sparse_prefill_config4_rows():
     """s_kv 32768, topk 2048, h_q 128, causal-valid indices (query t draws from [0, 28672 + t]): a slice of query
     rows at the full KV size is checked against the oracle."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_prefill_inputs(48, 128, 32768, 2048, causal_base=28672, seed=0, device="cpu")
     ref = attention.sparse_prefill(d["q"], d["kv"], d["indices"], 576 ** -0.5, 512, row_chunk=8)
     out, mx, lse = _prefill(d["q"].to(DEV), d["kv"].to(DEV), d["indices"].to(DEV), 576 ** -0.5)
@@ -202,7 +202,7 @@ def test_sparse_decode_many_requests_per_partition(ragged):
     """More requests than SM partitions: every CTA pair walks several requests (and, with per-request lengths,
     partitions that split requests), so the hand-over of Q, of the K ring and of the accumulators between
     requests is what this checks; two runs must agree bit for bit."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     b, h_q, s_kv, topk = 190, 128, 1024, 256
     d = W.sparse_decode_inputs(b, 1, h_q, s_kv, topk, seed=11, device="cpu")
     kv_deq = quant.dequantize_v32(d["kv_fp8"])
@@ -219,7 +219,7 @@ def test_sparse_decode_many_requests_per_partition(ragged):
 def test_sparse_prefill_many_query_tokens_per_cta_pair():
     """More query tokens than CTA pairs: every pair strides over several tokens, each with its own Q hand-over
     through the K ring; two runs must agree bit for bit."""
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     d = W.sparse_prefill_inputs(333, 128, 2048, 384, seed=9, device="cpu")
     ref = attention.sparse_prefill(d["q"], d["kv"], d["indices"], 576 ** -0.5, 512)
     args = (d["q"].to(DEV), d["kv"].to(DEV), d["indices"].to(DEV), 576 ** -0.5)

@@ -24,7 +24,7 @@ def _rank_main(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     sys.path.insert(0, ROOT)
     import bench
-    from flashmla_b200 import workloads as W
+    from tests import workloads as W
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         b_total = 1024

@@ -16,7 +16,8 @@ DEV = "cuda:0"
 
 def _run_pair(b, s_q, h_q, seqlens, seed):
     import flashmla_b200 as fm
-    from flashmla_b200 import _capi, workloads as W
+    from flashmla_b200 import _capi
+    from tests import workloads as W
     from flashmla_b200.flash_mla_interface import _make_sched_meta
     lib = _capi.lib()
     seq = torch.tensor(seqlens, dtype=torch.int32)

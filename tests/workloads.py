@@ -1,16 +1,24 @@
 """Seeded synthetic inputs with the shapes and value distributions of the benchmark configurations
 (dense decode at the DeepSeek-V3 serving shape, sparse FP8 decode, token-sparse prefill, the
-long-context batch-sharded sweep).  Used by bench.py and the tests; data is random-normal, no
-dataset is involved.
+long-context batch-sharded sweep).  Used by the tests, bench.py and the smoke run; data is random-normal, no
+dataset is involved.  Test and benchmark infrastructure: not part of the shipped package.
 """
 import math
 from typing import Dict, Optional
 
 import torch
 
-from .kvcache import quantize_fp8_kvcache
-
 BLOCK = 64
+
+
+def quantize_fp8_kvcache(blocked_k: torch.Tensor, pow2_scale: bool = False, pad_rows: int = 0) -> torch.Tensor:
+    """656-byte FP8 records of a bf16 cache: CUDA tensors through the library's cache-write kernel, CPU tensors
+    (fixtures that a CPU checker must see bit for bit) through the oracle's quantiser."""
+    if blocked_k.is_cuda:
+        from flashmla_b200.kvcache import quantize_fp8_kvcache as gpu_quantize
+        return gpu_quantize(blocked_k, pow2_scale, pad_rows)
+    from oracle import quant
+    return quant.quantize_v32(blocked_k, pow2_scale=pow2_scale, pad_rows=pad_rows)
 
 
 def _gen(seed: int, device="cpu") -> torch.Generator:
