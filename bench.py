@@ -9,8 +9,12 @@ dense BF16 MLA decode at the DeepSeek-V3 serving shape (batch 128 per GPU, h_q 1
 own batch on its own GPU (batch-sharded replicas, no collective on the data path), time is the maximum
 over ranks and `value` the aggregate over all GPUs.
 
---impl reference times the CPU restatement of the reference's torch attention (oracle/) on the host cores
-on a bounded sample of the same workload.
+A pass takes a fraction of a millisecond, so every one of the K timed steps replays the pass R times back to back
+(R chosen so that a step lasts about 20 ms) between one pair of CUDA events and reports elapsed / R.
+
+--impl reference times the reference's torch attention on the host cores on a bounded sample of the same workload:
+the CPU restatement under oracle/, or the unmodified function of a FlashMLA checkout when FLASHMLA_REFERENCE_DIR
+names one.
 """
 import argparse
 import json
@@ -26,6 +30,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D_QK, D_V = 576, 512
+# acceptance bounds of the benchmark specification (the same numbers as tests/helpers.py)
+OUT_COS_TOL, OUT_ABS_TOL, LSE_TOL = 1e-5, 2e-2, 1e-3
+TARGET_STEP_MS = 20.0
+L2_NOTE = "KV cache (> L2) streamed once per pass; q/out may stay in L2 between replays, see ms_per_step_cold_l2"
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -49,6 +57,14 @@ def reduce_over_ranks(ms_total, ms_e2e_total, units, tokens, flops, nbytes, dist
     sm = stats.clone()
     dist.all_reduce(sm, op=dist.ReduceOp.SUM)
     return float(mx[0]), float(mx[1]), float(sm[2]), float(sm[3]), float(sm[4]), float(sm[5])
+
+
+def max_over_ranks(values, dist, device):
+    if dist is None:
+        return list(values)
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
 
 
 def make_workload(name, device, seed, prefill_sq=4096):
@@ -84,6 +100,7 @@ def make_workload(name, device, seed, prefill_sq=4096):
         return dict(kind="sparse_decode", inputs=d, s_q=1, b=b, h_q=h_q, tokens=valid,
                     bytes=valid * 656 + b * h_q * D_QK * 2 + b * h_q * D_V * 2,
                     flops=2.0 * h_q * valid * (D_QK + D_V),
+                    flops_padded=2.0 * h_q * b * topk * (D_QK + D_V),      # the reference's convention counts the -1 slots too
                     desc=f"sparse fp8 MLA decode b={b} h_q={h_q} s_kv={s_kv} topk={topk} (5% padded -1) 656B records scale=amax/448")
     if name == "sparse_prefill":
         s_q, h_q, s_kv, topk = prefill_sq, 128, 32768, 2048
@@ -96,36 +113,21 @@ def make_workload(name, device, seed, prefill_sq=4096):
     raise SystemExit(f"unknown workload {name}")
 
 
-def run_step(w, sm_scale=D_QK ** -0.5, host=None):
-    """One pass through the public API.  With `host` (pinned host copies of the step's inputs) the inputs are
-    first copied to the device and the result is read back, all on the current stream."""
+def config_of(w):
+    """The `config` object of the JSON line: what is measured, identical for both arms."""
+    return {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": L2_NOTE}
+
+
+def run_step(w, sm_scale=D_QK ** -0.5):
+    """One pass through the public API on device-resident inputs."""
     import flashmla_b200 as fm
     d = w["inputs"]
     if w["kind"] == "dense":
-        q, bt, sl = d["q"], d["block_table"], d["cache_seqlens"]
-        if host is not None:
-            q = host["q"].to(q.device, non_blocking=True)
-            bt = host["block_table"].to(q.device, non_blocking=True)
-            sl = host["cache_seqlens"].to(q.device, non_blocking=True)
-            meta, _ = fm.get_mla_metadata()          # the sequence lengths are new: the schedule is recomputed
-        else:
-            meta = w["meta"]
-        out, lse = fm.flash_mla_with_kvcache(q, d["blocked_k"], bt, sl, D_V, meta, None, sm_scale, True)
+        out, lse = fm.flash_mla_with_kvcache(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], D_V, w["meta"], None, sm_scale, True)
     elif w["kind"] == "sparse_decode":
-        q, idx = d["q"], d["indices"]
-        if host is not None:
-            q = host["q"].to(q.device, non_blocking=True)
-            idx = host["indices"].to(q.device, non_blocking=True)
-        out, lse = fm.flash_mla_with_kvcache(q, d["kv_fp8"], None, None, D_V, w["meta"], None, sm_scale, False, True, idx)
+        out, lse = fm.flash_mla_with_kvcache(d["q"], d["kv_fp8"], None, None, D_V, w["meta"], None, sm_scale, False, True, d["indices"])
     else:
-        q, idx = d["q"], d["indices"]
-        if host is not None:
-            q = host["q"].to(q.device, non_blocking=True)
-            idx = host["indices"].to(q.device, non_blocking=True)
-        out, _, lse = fm.flash_mla_sparse_fwd(q, d["kv"], idx, sm_scale)
-    if host is not None:
-        host["out"].copy_(out, non_blocking=True)
-        host["lse"].copy_(lse, non_blocking=True)
+        out, _, lse = fm.flash_mla_sparse_fwd(d["q"], d["kv"], d["indices"], sm_scale)
     return out, lse
 
 
@@ -152,15 +154,19 @@ class E2EPipeline:
     memory to the device and reads its result back.  Consecutive steps are independent, so they are software-pipelined
     over three streams (copy in / compute / copy out) with double-buffered device inputs and host outputs: the copy
     engines of both directions and the SMs work at the same time, as in a serving loop that prepares the next batch
-    while the current one runs."""
+    while the current one runs.  With compute=False only the copies run (the same bytes, no kernel): the ceiling the
+    host link sets for the end-to-end figure."""
 
-    def __init__(self, w, host):
-        self.w, self.host = w, host
+    def __init__(self, w, host, compute=True):
+        self.w, self.host, self.compute = w, host, compute
         dev = w["inputs"]["q"].device
         self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
         self.keys = [k for k in host if k not in ("out", "lse")]
         self.dev_in = [{k: torch.empty_like(host[k], device=dev) for k in self.keys} for _ in range(2)]
         self.host_out = [{k: torch.empty_like(host[k]).pin_memory() for k in ("out", "lse")} for _ in range(2)]
+        self.dev_out = None
+        if not compute:
+            self.dev_out = {k: torch.empty_like(host[k], device=dev) for k in ("out", "lse")}
         self.cmp_done = [None, None]
         self.out_done = [None, None]
         self.keep = [None, None]
@@ -178,7 +184,9 @@ class E2EPipeline:
         with torch.cuda.stream(self.s_cmp):
             self.s_cmp.wait_event(in_done)
             x = self.dev_in[slot]
-            if w["kind"] == "dense":
+            if not self.compute:
+                out, lse = self.dev_out["out"], self.dev_out["lse"]
+            elif w["kind"] == "dense":
                 meta, _ = fm.get_mla_metadata()                    # the sequence lengths are new: the schedule is recomputed
                 out, lse = fm.flash_mla_with_kvcache(x["q"], d["blocked_k"], x["block_table"], x["cache_seqlens"], D_V, meta,
                                                      None, D_QK ** -0.5, True)
@@ -207,6 +215,21 @@ class E2EPipeline:
             self.step(i)
         for st in (self.s_in, self.s_cmp, self.s_out):
             cur.wait_stream(st)
+
+    def timed(self, steps, reps, barrier):
+        """K steps, each `reps` pipelined passes between one event pair; returns the mean milliseconds per pass."""
+        self.run(3)
+        barrier()
+        total = 0.0
+        for _ in range(steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            self.run(reps)
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1) / reps
+        barrier()
+        return total / steps
 
 
 class KernelTimer:
@@ -297,32 +320,105 @@ def measured_peaks():
     return dict(hbm=6650.0, tflops=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
+def captured_traffic(workload):
+    """DRAM bytes per launch of the workload's main kernel from the ncu capture summarised under profiles/
+    (dram__bytes_read.sum + dram__bytes_write.sum); the small JSON beside the summary names the commit it was taken at."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        rec = json.load(open(path)).get(workload)
+    except (OSError, ValueError):
+        return None, None
+    if not rec:
+        return None, None
+    return float(rec["dram_bytes_per_launch"]), rec.get("captured_at_commit")
+
+
+def bind_to_gpu_numa_node(gpu_index):
+    """Pins this process (and, by first touch, its pinned host buffers) to the cores nvidia-smi lists as closest to the
+    GPU.  Read-only query; returns a short description for the JSON line."""
+    try:
+        txt = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+    except Exception as exc:
+        return f"unbound ({type(exc).__name__})"
+    header = None
+    for ln in txt.splitlines():
+        cols = [c.strip() for c in ln.split("\t") if c.strip() != ""]
+        if not cols:
+            continue
+        if header is None and any("CPU Affinity" in c for c in cols):
+            header = cols
+            continue
+        if header is not None and cols[0] == f"GPU{gpu_index}":
+            # the row has one more leading cell (its own name) than the header has GPU/NIC columns
+            try:
+                aff = cols[1 + header.index("CPU Affinity")] if header[0] != "" else cols[header.index("CPU Affinity")]
+            except (ValueError, IndexError):
+                return "unbound (no affinity column)"
+            cores = set()
+            for part in aff.split(","):
+                part = part.strip()
+                if "-" in part:
+                    a, b = part.split("-")
+                    cores.update(range(int(a), int(b) + 1))
+                elif part.isdigit():
+                    cores.add(int(part))
+            allowed = cores & set(os.sched_getaffinity(0))
+            if not allowed:
+                return f"unbound (affinity {aff} not available to this process)"
+            os.sched_setaffinity(0, allowed)
+            return f"cores {aff}"
+    return "unbound (GPU row not found)"
+
+
 # ------------------------------------------------------------------------------------------------------
-# CPU arm: the oracle (port of the reference's torch attention) on the host cores, bounded sample
+# CPU arm: the reference's torch attention on the host cores, bounded sample.  Returns the checker's outputs too, so
+# that the timed GPU result can be compared with them.
 # ------------------------------------------------------------------------------------------------------
-def cpu_baseline(w, budget_s=15.0):
+def _reference_dense_fn():
+    """(function, kind): the unmodified reference_torch of a FlashMLA checkout named by FLASHMLA_REFERENCE_DIR
+    (its tests/test_flash_mla_dense_decoding.py:73-141), else the restatement under oracle/."""
+    ref_dir = os.environ.get("FLASHMLA_REFERENCE_DIR")
+    if ref_dir and os.path.exists(os.path.join(ref_dir, "tests", "test_flash_mla_dense_decoding.py")):
+        try:
+            import types
+            sys.modules.setdefault("flash_mla", types.ModuleType("flash_mla"))
+            sys.path.insert(0, os.path.join(ref_dir, "tests"))
+            import test_flash_mla_dense_decoding as ref_mod
+            return (lambda q, kc, bt, sl, dv, causal: ref_mod.reference_torch(sl, bt, q, kc, dv, causal)), "reference"
+        except Exception as exc:
+            print(f"bench.py: FLASHMLA_REFERENCE_DIR is set but its test module does not import ({exc}); using oracle/", file=sys.stderr)
+    from oracle import attention
+    return attention.dense_decode, "port"
+
+
+def cpu_baseline(w, budget_s=15.0, keep_outputs=False):
     from oracle import attention, quant
-    cores = os.cpu_count() or 1
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     torch.set_num_threads(cores)
     d = w["inputs"]
+    outs = {}
+    kind = "port"
     if w["kind"] == "dense":
+        dense_fn, kind = _reference_dense_fn()
         b = w["b"]
-        order = [0] + list(range(1, b))
-        q, bk, bt, sl = d["q"].cpu(), None, d["block_table"].cpu(), d["cache_seqlens"].cpu()
+        q, bt, sl = d["q"].cpu(), d["block_table"].cpu(), d["cache_seqlens"].cpu()
         done_tokens, t_used, n_req = 0, 0.0, 0
-        for i in order:
+        for i in range(b):
             pages = bt[i, :(int(sl[i]) + 63) // 64].long()
             kv_i = d["blocked_k"][pages.to(d["blocked_k"].device)].cpu()
             bt_i = torch.arange(pages.numel(), dtype=torch.int32).view(1, -1)
             t0 = time.perf_counter()
-            attention.dense_decode(q[i:i + 1], kv_i, bt_i, sl[i:i + 1], D_V, True)
+            o, l = dense_fn(q[i:i + 1], kv_i, bt_i, sl[i:i + 1], D_V, True)
             t_used += time.perf_counter() - t0
+            if keep_outputs:
+                outs[i] = (o, l)
             done_tokens += int(sl[i])
             n_req += 1
             if t_used > budget_s:
                 break
         frac = done_tokens / w["tokens"]
-        sample = f"{n_req} of {b} requests ({done_tokens} of {w['tokens']} KV tokens), oracle.attention.dense_decode"
+        name = "reference_torch of the FlashMLA checkout" if kind == "reference" else "oracle.attention.dense_decode"
+        sample = f"{n_req} of {b} requests ({done_tokens} of {w['tokens']} KV tokens), {name}"
     elif w["kind"] == "sparse_decode":
         b = w["b"]
         t_used, n_req = 0.0, 0
@@ -336,8 +432,10 @@ def cpu_baseline(w, budget_s=15.0):
             qi = d["q"][i:i + 1].cpu()
             t0 = time.perf_counter()
             kv_deq = quant.dequantize_v32(kv_raw)
-            attention.sparse_decode(qi, kv_deq, idx_s, D_QK ** -0.5, D_V)
+            o, l = attention.sparse_decode(qi, kv_deq, idx_s, D_QK ** -0.5, D_V)
             t_used += time.perf_counter() - t0
+            if keep_outputs:
+                outs[i] = (o, l)
             n_req += 1
             if t_used > budget_s:
                 break
@@ -351,12 +449,32 @@ def cpu_baseline(w, budget_s=15.0):
             r1 = min(rows + 16, w["s_q"])
             qi, ii = q[rows:r1].cpu(), idx[rows:r1].cpu()
             t0 = time.perf_counter()
-            attention.sparse_prefill(qi, kv, ii, D_QK ** -0.5, D_V, row_chunk=16)
+            o, _, l = attention.sparse_prefill(qi, kv, ii, D_QK ** -0.5, D_V, row_chunk=16)
             t_used += time.perf_counter() - t0
+            if keep_outputs:
+                for r in range(rows, r1):
+                    outs[r] = (o[r - rows:r - rows + 1], l[r - rows:r - rows + 1])
             rows = r1
         frac = rows / w["s_q"]
         sample = f"{rows} of {w['s_q']} query rows, oracle.attention.sparse_prefill"
-    return dict(seconds=t_used, frac=frac, cores=cores, sample=sample)
+    return dict(seconds=t_used, frac=frac, cores=cores, sample=sample, kind=kind, outputs=outs)
+
+
+def check_against_oracle(w, out, lse, oracle_outputs):
+    """Compares the TIMED result (the output of the replayed graph) with the checker's outputs, unit by unit (request /
+    query row); raises on the first unit outside the acceptance bounds.  Returns the number of units checked."""
+    from oracle.compare import cos_diff, max_abs_err
+    out_c, lse_c = out.detach().cpu(), lse.detach().cpu()
+    for i, (o_ref, l_ref) in oracle_outputs.items():
+        o, l = out_c[i:i + 1], lse_c[i:i + 1]
+        cd = abs(cos_diff(o.float(), o_ref.float()))
+        mae = max_abs_err(o, o_ref)
+        fin = torch.isfinite(l_ref)
+        le = float((l[fin] - l_ref[fin]).abs().max()) if fin.any() else 0.0
+        if not (cd <= OUT_COS_TOL and mae <= OUT_ABS_TOL and le <= LSE_TOL and torch.equal(torch.isinf(l), torch.isinf(l_ref))):
+            raise SystemExit(f"bench.py: the timed result of unit {i} is outside the acceptance bounds "
+                             f"(cosine deficit {cd:.2e}, max abs {mae:.2e}, lse {le:.2e})")
+    return len(oracle_outputs)
 
 
 def metric_of(w):
@@ -376,6 +494,7 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill"])
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--replays", type=int, default=0, help="passes per timed step (0: as many as make a step last about 20 ms)")
     ap.add_argument("--prefill-sq", type=int, default=4096, help="query tokens of the sparse_prefill workload (smaller for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -398,10 +517,12 @@ def main():
                 vals.append(units_per_step * r["frac"] / r["seconds"])
         v = sum(vals) / len(vals)
         line = {"impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-                "warmup": args.warmup, "ms_per_step": 1e3 * units_per_step / v, "higher_is_better": True, "scaling": "weak",
+                "warmup": args.warmup, "ms_per_step": 1e3 * units_per_step / v, "higher_is_better": True,
+                "scaling": "strong" if args.workload == "longctx" else "weak",
                 "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": w["desc"], "note": "CPU port of the reference's torch attention (oracle/), bounded sample, extrapolated to a full step"},
-                "cpu_baseline": {"value": v, "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "config": config_of(w),
+                "note": "the reference's torch attention on the host cores, bounded sample, extrapolated to a full step",
+                "cpu_baseline": {"value": v, "unit": unit, "cores": r["cores"], "kind": r["kind"], "sample": r["sample"]},
                 "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
         return
@@ -412,6 +533,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = bind_to_gpu_numa_node(local_rank)          # before any pinned buffer is allocated
+    os.environ.setdefault("OMP_NUM_THREADS", str(len(os.sched_getaffinity(0))))
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -427,27 +551,45 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing ------------------------------------------------------------------------
+    # ---- warm-up, and how many passes make a step of about 20 ms (the same R on every rank) ----------------
     for _ in range(args.warmup):
         run_step(w)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        run_step(w)
+    e1.record()
+    torch.cuda.synchronize()
+    est_ms = max_over_ranks([e0.elapsed_time(e1) / 5], dist, dev)[0]
+    reps = args.replays if args.replays > 0 else max(1, min(400, int(round(TARGET_STEP_MS / max(est_ms, 1e-3)))))
+
+    # ---- eager launches: K steps of R passes, with an event pair around every kernel of the first pass of a step ------
     timer = KernelTimer()
     barrier()
-    with ClockSampler(local_rank) as clocks:
-        fmi.set_kernel_timer(timer)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+    ms_eager = 0.0
+    with ClockSampler(local_rank) as clocks_eager:
         for _ in range(args.steps):
-            run_step(w)
-        e1.record()
+            fmi.set_kernel_timer(timer)
+            run_step(w)                                            # per-kernel times (not part of the step's own clock)
+            fmi.set_kernel_timer(None)
+            e0.record()
+            for _ in range(reps):
+                run_step(w)
+            e1.record()
+            torch.cuda.synchronize()
+            ms_eager += e0.elapsed_time(e1) / reps
         barrier()
-        fmi.set_kernel_timer(None)
-    ms_eager = e0.elapsed_time(e1)
+    ms_eager /= args.steps
     kernel_ms = timer.mean_ms()
-    launches = timer.launches()
+    launches_per_pass = timer.launches() // args.steps
+    clocks = clocks_eager
 
-    # ---- the same steps as a CUDA graph: one step is captured once and replayed (a decode loop is launch-bound between
-    # its kernels; the API neither allocates outside torch's allocator nor synchronises, so it can be captured) --------
-    ms_total, launch_mode = ms_eager, "eager launches"
+    # ---- the same pass as a CUDA graph: captured once and replayed (a decode loop is launch-bound between its kernels;
+    # the API neither allocates outside torch's allocator nor synchronises, so it can be captured) ----------------------
+    ms_step, launch_mode = ms_eager, "eager launches"
+    ms_cold = None
+    g_out = g_lse = None
     try:
         eager_out, eager_lse = run_step(w)
         graph = torch.cuda.CUDAGraph()
@@ -456,44 +598,63 @@ def main():
         for _ in range(3):
             graph.replay()
         barrier()
-        with ClockSampler(local_rank) as clocks:
-            e0.record()
+        total = 0.0
+        with ClockSampler(local_rank) as clocks_graph:
             for _ in range(args.steps):
-                graph.replay()
-            e1.record()
+                e0.record()
+                for _ in range(reps):
+                    graph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                total += e0.elapsed_time(e1) / reps
             barrier()
         if not (torch.equal(g_out.view(torch.int16), eager_out.view(torch.int16)) and torch.equal(g_lse, eager_lse)):
             raise RuntimeError("graph replay and eager launch disagree")
-        ms_total, launch_mode = e0.elapsed_time(e1), "CUDA graph replay of one step"
+        ms_step, launch_mode, clocks = total / args.steps, "CUDA graph replay of one pass", clocks_graph
+        # the same pass with a cold L2: 512 MB are overwritten before every single timed replay (the method of the
+        # reference's tests/kernelkit/bench.py:166-205)
+        scrub = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+        total = 0.0
+        for _ in range(args.steps):
+            scrub.fill_(1)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        ms_cold = total / args.steps
+        del scrub
     except Exception as exc:                      # capture is an optimisation of the launch path, never a requirement
         print(f"bench.py: CUDA graph capture not used ({exc})", file=sys.stderr)
+        g_out, g_lse = run_step(w)
+        torch.cuda.synchronize()
 
-    # ---- end-to-end timing: host buffers in, result out --------------------------------------------------
+    # ---- end-to-end timing: host buffers in, result out; and the copies alone ---------------------------------
     host, h2d, d2h = make_host_buffers(w)
+    reps_e2e = max(1, min(reps, int(round(TARGET_STEP_MS / max(3 * est_ms, 1e-3)))))
     pipe = E2EPipeline(w, host)
-    pipe.run(3)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    pipe.run(args.steps)
-    f1.record()
-    barrier()
-    ms_e2e_total = f0.elapsed_time(f1)
+    solo_ms = None
+    if dist is not None:
+        # rank 0 alone first (the others wait): what one GPU reaches when it has the host to itself
+        if rank == 0:
+            solo_ms = pipe.timed(max(3, args.steps // 4), reps_e2e, lambda: torch.cuda.synchronize())
+        barrier()
+    ms_e2e = pipe.timed(args.steps, reps_e2e, barrier)
     out_chk, lse_chk = run_step(w)                                  # the pipelined path returns the same result
     torch.cuda.synchronize()
-    last = pipe.host_out[(args.steps - 1) & 1]
+    last = pipe.host_out[(reps_e2e - 1) & 1]
     if not (torch.equal(last["out"].view(torch.int16), out_chk.cpu().view(torch.int16)) and torch.equal(last["lse"], lse_chk.cpu())):
         raise SystemExit("bench.py: the end-to-end leg returned a different result than the device-resident leg")
+    ms_copy = E2EPipeline(w, host, compute=False).timed(max(3, args.steps // 2), reps_e2e, barrier)
 
     # ---- reduce over ranks ---------------------------------------------------------------------------------
-    ms_total, ms_e2e_total, units_all, tokens_all, flops_all, bytes_all = reduce_over_ranks(
-        ms_total, ms_e2e_total, units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"]), dist, dev)
+    ms_step_all, ms_e2e_all, units_all, tokens_all, flops_all, bytes_all = reduce_over_ranks(
+        ms_step, ms_e2e, units_per_step, float(w["tokens"]), w["flops"], float(w["bytes"]), dist, dev)
+    ms_eager_all, ms_copy_all, ms_cold_all = max_over_ranks([ms_eager, ms_copy, ms_cold if ms_cold is not None else -1.0], dist, dev)
     if rank != 0:
         dist.destroy_process_group()
         return
 
-    ms_step = ms_total / args.steps
-    ms_e2e = ms_e2e_total / args.steps
     peaks = measured_peaks()
     main_kernel = {"dense": "mla_dense_decode_fwd", "sparse_decode": "mla_sparse_decode_fwd",
                    "sparse_prefill": "mla_sparse_prefill_fwd"}[w["kind"]]
@@ -503,33 +664,48 @@ def main():
     else:
         roof = {"bound": "tensor", "achieved": w["flops"] / 1e12 / (k_ms / 1e3), "peak": peaks["tflops"], "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
-    # DRAM traffic per launch from the ncu capture summarised under profiles/ (dram__bytes_read + write): only the
-    # default dense workload has been captured; traffic scales with the workload's bytes, so it is given per launch
-    # of exactly that workload and left null otherwise.
-    roof["traffic"] = 681.9e6 if (args.workload == "dense" and world == 1) else None
+    traffic, traffic_commit = captured_traffic(args.workload) if world == 1 else (None, None)
+    roof["traffic"] = traffic
+    roof["traffic_captured_at_commit"] = traffic_commit
     roof["kernel"] = main_kernel
     roof["kernel_ms"] = k_ms
     roof["peak_source"] = peaks["source"]
 
+    clk = clocks.summary()
+    e2e = {"value": units_all / (ms_e2e_all / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "ms_per_step": ms_e2e_all, "replays_per_step": reps_e2e,
+           "pipelining": "passes overlapped on 3 streams (copy in / compute / copy out), double-buffered",
+           "host_binding": numa,
+           "copy_only": {"ms_per_step": ms_copy_all, "per_rank_gbs": (h2d + d2h) / 1e9 / (ms_copy_all / 1e3),
+                         "aggregate_gbs": world * (h2d + d2h) / 1e9 / (ms_copy_all / 1e3),
+                         "what": "the same host<->device copies with no kernel between them: the host link's ceiling for this figure"}}
+    if solo_ms is not None:
+        e2e["ms_per_step_rank0_alone"] = solo_ms
+        e2e["e2e_efficiency_vs_n1"] = solo_ms / ms_e2e_all
     line = {
-        "metric": metric, "value": units_all / (ms_step / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "metric": metric, "value": units_all / (ms_step_all / 1e3), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step_all, "higher_is_better": True,
         "scaling": "strong" if args.workload == "longctx" else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": "inputs larger than L2 (KV cache streamed once per step)",
-                   "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel], "launch": launch_mode},
-        "ms_per_step_eager": ms_eager / args.steps,
-        "tflops": flops_all / 1e12 / (ms_step / 1e3), "hbm_gbs": bytes_all / 1e9 / (ms_step / 1e3),
-        "kv_tokens_per_s": tokens_all / (ms_step / 1e3),
-        "kernel_ms": kernel_ms, "gpu_launches": launches,
-        "roofline": roof, "clocks": clocks.summary(),
-        "e2e": {"value": units_all / (ms_e2e / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e, "pipelining": "steps overlapped on 3 streams (copy in / compute / copy out), double-buffered"},
+        "config": config_of(w),
+        "kernel": {0: "auto", 1: "portable", 2: "tcgen05"}[args.kernel], "launch": launch_mode, "replays_per_step": reps,
+        "ms_per_step_eager": ms_eager_all,
+        "ms_per_step_cold_l2": ms_cold_all if ms_cold_all >= 0 else None,
+        "ms_x_sm_ghz": ms_step_all * clk["sm_mhz"] / 1e3 if clk["sm_mhz"] else None,
+        "tflops": flops_all / 1e12 / (ms_step_all / 1e3), "hbm_gbs": bytes_all / 1e9 / (ms_step_all / 1e3),
+        "kv_tokens_per_s": tokens_all / (ms_step_all / 1e3),
+        "kernel_ms": kernel_ms, "gpu_launches": launches_per_pass * reps * args.steps,
+        "roofline": roof, "clocks": clk, "e2e": e2e,
     }
-    if not args.no_cpu_baseline and world >= 1:
-        r = cpu_baseline(w, budget_s=12.0)
+    if "flops_padded" in w:
+        line["tflops_reference_convention"] = world * w["flops_padded"] / 1e12 / (ms_step_all / 1e3)
+    if not args.no_cpu_baseline and world == 1:
+        r = cpu_baseline(w, budget_s=12.0, keep_outputs=True)
         line["cpu_baseline"] = {"value": units_per_step * r["frac"] / r["seconds"], "unit": unit, "cores": r["cores"],
-                                "kind": "port", "sample": r["sample"]}
+                                "kind": r["kind"], "sample": r["sample"]}
+        # the result that was timed (the replayed graph's output) against the checker, unit by unit
+        line["parity_checked"] = check_against_oracle(w, g_out, g_lse, r["outputs"])
+        line["parity_bounds"] = {"out_cos_deficit": OUT_COS_TOL, "out_max_abs": OUT_ABS_TOL, "lse_abs": LSE_TOL}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

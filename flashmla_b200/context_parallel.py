@@ -33,6 +33,36 @@ def partials_to_split_layout(outs: torch.Tensor, lses: torch.Tensor) -> Tuple[to
     return o_accum, lse_accum, num_splits
 
 
+def merge_kv_shard_partials(outs: torch.Tensor, lses: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merges the partial results of `world` KV shards with the library's combine kernel (mla_combine).
+
+    outs [world, b, s_q, h_q, d_v], lses [world, b, h_q, s_q] (natural log; +/-inf where a shard holds nothing of a
+    request), both CUDA tensors on one device - the all-gathered results of the ranks, or partials computed one after
+    the other on a single GPU.  Returns (out [b, s_q, h_q, d_v] in out_dtype, lse [b, h_q, s_q] fp32)."""
+    if not outs.is_cuda:
+        raise RuntimeError("flashmla_b200 runs on CUDA devices only (there is no CPU path)")
+    if out_dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError("out_dtype must be bfloat16 or float16")
+    world, b, s_q, h_q, d_v = outs.shape
+    o_accum, lse_accum, num_splits = partials_to_split_layout(outs, lses)
+    out = torch.empty((b, s_q, h_q, d_v), dtype=out_dtype, device=outs.device)
+    lse = torch.empty((b, h_q, s_q), dtype=torch.float32, device=outs.device)
+    if world == 1:
+        out.copy_(outs[0])
+        lse.copy_(lses[0])
+        return out, lse
+    with torch.cuda.device(outs.device):
+        c = _capi.CombineArgs(
+            b=b, s_q=s_q, h_q=h_q, d_v=d_v,
+            lse=_capi.ptr(lse), lse_stride_b=lse.stride(0), lse_stride_s=lse.stride(2), lse_stride_h=lse.stride(1),
+            out=_capi.ptr(out), o_stride_b=out.stride(0), o_stride_s=out.stride(1), o_stride_h=out.stride(2),
+            lse_accum=_capi.ptr(lse_accum), o_accum=_capi.ptr(o_accum), num_splits=_capi.ptr(num_splits), attn_sink=None,
+            dtype=_capi.MLA_DTYPE_FP16 if out_dtype == torch.float16 else _capi.MLA_DTYPE_BF16,
+            stream=torch.cuda.current_stream(outs.device).cuda_stream)
+        _capi.check(_capi.lib().mla_combine(c), "mla_combine")
+    return out, lse
+
+
 def flash_mla_decode_kv_sharded(q: torch.Tensor, k_cache: torch.Tensor, block_table: torch.Tensor,
                                 cache_seqlens: torch.Tensor, head_dim_v: int, softmax_scale: Optional[float] = None,
                                 group=None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -49,20 +79,8 @@ def flash_mla_decode_kv_sharded(q: torch.Tensor, k_cache: torch.Tensor, block_ta
     out_r, lse_r = flash_mla_with_kvcache(q, k_cache, block_table, cache_seqlens, head_dim_v, meta, None, softmax_scale, False)
     if world == 1:
         return out_r, lse_r
-    b, s_q, h_q, d_v = out_r.shape
     outs = torch.empty((world,) + tuple(out_r.shape), dtype=out_r.dtype, device=q.device)
     lses = torch.empty((world,) + tuple(lse_r.shape), dtype=lse_r.dtype, device=q.device)
     dist.all_gather_into_tensor(outs, out_r.contiguous(), group=group)
     dist.all_gather_into_tensor(lses, lse_r.contiguous(), group=group)
-    o_accum, lse_accum, num_splits = partials_to_split_layout(outs, lses)
-    out = torch.empty((b, s_q, h_q, d_v), dtype=q.dtype, device=q.device)
-    lse = torch.empty((b, h_q, s_q), dtype=torch.float32, device=q.device)
-    with torch.cuda.device(q.device):
-        c = _capi.CombineArgs(
-            b=b, s_q=s_q, h_q=h_q, d_v=d_v,
-            lse=_capi.ptr(lse), lse_stride_b=lse.stride(0), lse_stride_s=lse.stride(2), lse_stride_h=lse.stride(1),
-            out=_capi.ptr(out), o_stride_b=out.stride(0), o_stride_s=out.stride(1), o_stride_h=out.stride(2),
-            lse_accum=_capi.ptr(lse_accum), o_accum=_capi.ptr(o_accum), num_splits=_capi.ptr(num_splits), attn_sink=None,
-            stream=torch.cuda.current_stream().cuda_stream)
-        _capi.check(_capi.lib().mla_combine(c), "mla_combine")
-    return out, lse
+    return merge_kv_shard_partials(outs, lses, q.dtype)

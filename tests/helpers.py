@@ -49,3 +49,65 @@ def non_contiguousify(t: torch.Tensor) -> torch.Tensor:
     view = base[tuple(slice(0, d) for d in t.shape)]
     view[:] = t
     return view
+
+
+def check_schedule_properties(meta, num_splits, eff_seqlens, num_sm_parts, block_size_n, fixed_overhead):
+    """Size-independent properties of a tile schedule (metadata rows + num_splits), whoever produced it:
+      * every scheduling block of every request is covered exactly once, in order, by the partitions' ranges
+        (a zero-length request counts one block for the budget and is visited by exactly one partition);
+      * num_splits is the prefix sum of the number of partitions that touch each request; begin_split_idx is the
+        number of earlier partitions that touched the partition's first request;
+      * the split flags are 0 / 1 and say exactly whether more than one partition touches the first / last request
+        (both flags carry the same value when a partition holds a single request);
+      * no partition exceeds the budget ceil(total / P) + F, where every visited request costs F on top of its blocks;
+      * partitions that start after the last request report begin_req_idx == b and come last.
+    `eff_seqlens` are the lengths the scheduler balances on (oracle.sched_meta.effective_seqlens).
+    Follows the consumers' reading of the metadata: csrc/sm90/decode/dense/splitkv_mla.cuh:1021-1033,1242."""
+    b = len(eff_seqlens)
+    nblk = [max(int(s) - 1, 0) // block_size_n + 1 for s in eff_seqlens]
+    total = sum(n + fixed_overhead for n in nblk)
+    payload = -(-total // num_sm_parts) + fixed_overhead
+    rows = [[int(x) for x in meta[p][:7]] for p in range(num_sm_parts)]
+    ns = [int(x) for x in num_splits]
+    assert len(ns) == b + 1 and ns[0] == 0
+    # pass 1: the block ranges
+    covered = [0] * b            # next uncovered block of each request
+    pieces = [[] for _ in range(b)]      # partitions that touch each request, in order
+    seen_inactive = False
+    for p, (begin_req, end_req, begin_block, end_block, begin_split, first_split, last_split) in enumerate(rows):
+        if begin_req >= b:
+            assert begin_req == b, f"partition {p}: inactive partitions must report begin_req_idx == b"
+            seen_inactive = True
+            continue
+        assert not seen_inactive, f"partition {p}: active partition after an inactive one"
+        assert 0 <= begin_req <= end_req < b, f"partition {p}: request range [{begin_req}, {end_req}]"
+        load = 0
+        for r in range(begin_req, end_req + 1):
+            sb = begin_block if r == begin_req else 0
+            end = end_block if r == end_req else nblk[r]
+            if int(eff_seqlens[r]) == 0:
+                assert sb == 0 and end in (0, 1), f"partition {p}: zero-length request {r} has range [{sb}, {end})"
+                assert not pieces[r], f"zero-length request {r} is visited twice"
+                covered[r] = nblk[r]
+                load += 1 + fixed_overhead
+            else:
+                assert sb == covered[r], f"partition {p}: request {r} starts at block {sb}, expected {covered[r]}"
+                assert sb < end <= nblk[r], f"partition {p}: request {r} has range [{sb}, {end}) of {nblk[r]} blocks"
+                covered[r] = end
+                load += (end - sb) + fixed_overhead
+            pieces[r].append(p)
+        assert load <= payload, f"partition {p}: load {load} exceeds the budget {payload}"
+    for r in range(b):
+        assert covered[r] == nblk[r], f"request {r}: blocks [{covered[r]}, {nblk[r]}) are not covered"
+        assert ns[r + 1] - ns[r] == len(pieces[r]), f"request {r}: {len(pieces[r])} pieces, num_splits says {ns[r + 1] - ns[r]}"
+    # pass 2: split indices and flags
+    for p, (begin_req, end_req, begin_block, end_block, begin_split, first_split, last_split) in enumerate(rows):
+        assert first_split in (0, 1) and last_split in (0, 1), f"partition {p}: flags {first_split}, {last_split}"
+        if begin_req >= b:
+            assert begin_split == 0 and first_split == 0 and last_split == 0, f"partition {p}: inactive partition with split state"
+            continue
+        assert begin_split == pieces[begin_req].index(p), f"partition {p}: begin_split_idx {begin_split}"
+        first_is_split = int(len(pieces[begin_req]) > 1)
+        last_is_split = int(len(pieces[end_req]) > 1)
+        assert first_split == first_is_split, f"partition {p}: is_first_req_splitted {first_split}, request has {len(pieces[begin_req])} pieces"
+        assert last_split == last_is_split, f"partition {p}: is_last_req_splitted {last_split}, request has {len(pieces[end_req])} pieces"

@@ -118,6 +118,33 @@ def _gpu_rank(rank, world, port):
 
 
 @pytest.mark.gpu
+def test_kv_shard_merge_on_one_gpu():
+    """Everything of the KV-sharded path except the all_gather, on ONE GPU: the two shards' partials are computed one
+    after the other through the ordinary decode API, stacked as the gather would deliver them, and merged by the
+    library's combine kernel (merge_kv_shard_partials, the function the multi-rank path calls after its all_gather)."""
+    sys.path.insert(0, ROOT)
+    import flashmla_b200 as fm
+    from flashmla_b200.context_parallel import merge_kv_shard_partials
+    dev = torch.device("cuda", 0)
+    q, kv, _ = _case(seed=1, b=3, h_q=128, lens=(5000, 64, 9000))
+    cut = [2500, 64, 1000]
+    outs, lses = [], []
+    for rank in range(2):
+        mine = [k[:c] if rank == 0 else k[c:] for k, c in zip(kv, cut)]
+        cache, table, lens = _paged(mine)
+        meta, _ = fm.get_mla_metadata()
+        o, l = fm.flash_mla_with_kvcache(q.to(dev), cache.to(dev), table.to(dev), lens.to(dev), 512, meta, None, None, False)
+        outs.append(o)
+        lses.append(l)
+    out, lse = merge_kv_shard_partials(torch.stack(outs), torch.stack(lses))
+    torch.cuda.synchronize()
+    fm.check_status()
+    ref_out, ref_lse = _full_reference(q, kv)
+    assert (out.cpu().float() - ref_out.float()).abs().max() <= 2e-2
+    assert (lse.cpu() - ref_lse).abs().max() <= 1e-3
+
+
+@pytest.mark.gpu
 def test_kv_sharded_decode_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -81,9 +81,9 @@ def test_many_splits_long_sequence():
     _case(3, 1, 128, 1, [20000, 64, 300], False, seed=5)
 
 
-def test_serving_shape_sample():
+def test_serving_shape_every_request():
     """Serving shape (batch 128, h_q 128, seqlens ~ N(4096, 512^2) clipped to [1, 8192], one forced to 8192,
-    causal, s_q in {1, 2}): the full batch runs on the GPU, a sample of requests is checked against the oracle."""
+    causal, s_q in {1, 2}): the full batch runs on the GPU and EVERY request is checked against the oracle."""
     from tests import workloads as W
     import flashmla_b200 as fm
     seq = W.seqlens_normal(128, 4096, 512, 1, 8192, True, seed=0)
@@ -94,15 +94,47 @@ def test_serving_shape_sample():
                                              d["cache_seqlens"].to(DEV), 512, meta, None, causal=True)
         torch.cuda.synchronize()
         fm.check_status()
-        sample = [0, 1, 17, 63, 127]
-        ref_out, ref_lse = attention.dense_decode(d["q"][sample], d["blocked_k"], d["block_table"][sample],
-                                                  d["cache_seqlens"][sample], 512, True)
-        assert_out_close("out", out[sample], ref_out)
-        assert_lse_close("lse", lse[sample], ref_lse)
+        ref_out, ref_lse = attention.dense_decode(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], 512, True)
+        assert_out_close("out", out, ref_out)
+        assert_lse_close("lse", lse, ref_lse)
         # size-independent properties over the whole batch: finite results, and since a softmax output is a
         # convex combination of value rows, |out| is bounded by the largest |value| of the cache
         assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
         assert out.float().abs().max() <= d["blocked_k"].float().abs().max()
+
+
+def test_fp16_inputs():
+    """q and the cache in fp16 (the reference accepts both 16-bit types: csrc/api/dense_decode.h:33): checked against
+    the oracle computed from the same fp16 values."""
+    from tests import workloads as W
+    seqlens = [140, 515, 20, 0, 64, 1, 1000, 65, 4096]
+    for s_q, h_q, causal in ((1, 128, False), (2, 128, True), (2, 16, True)):
+        d = W.dense_decode_inputs(torch.tensor(seqlens, dtype=torch.int32), s_q, h_q, 1, seed=31 + s_q, device="cpu", poison_unused=True)
+        q16, k16 = d["q"].to(torch.float16), d["blocked_k"].to(torch.float16)
+        ref_out, ref_lse = attention.dense_decode(q16, k16, d["block_table"], d["cache_seqlens"], 512, causal)
+        assert ref_out.dtype == torch.float16
+        out, lse = _run(q16.to(DEV), k16.to(DEV), d["block_table"].to(DEV), d["cache_seqlens"].to(DEV), 512, causal)
+        assert out.dtype == torch.float16
+        assert_out_close("out", out, ref_out)
+        assert_lse_close("lse", lse, ref_lse)
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+def test_sequence_longer_than_the_block_table(impl):
+    """A cache_seqlens entry beyond 64 * max_blocks_per_seq must not read the block table out of bounds: blocks
+    beyond the table's width have no page.  Results for such a request are unspecified (the reference would read out
+    of bounds); the other requests must be right and nothing may fault."""
+    from tests import workloads as W
+    seq = torch.tensor([300, 200, 64], dtype=torch.int32)
+    d = W.dense_decode_inputs(seq, 1, 128, 1, seed=41, device="cpu")
+    ref_out, ref_lse = attention.dense_decode(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], 512, False)
+    bad = seq.clone()
+    bad[1] = 64 * d["block_table"].size(1) + 1000                 # far beyond the table
+    out, lse = _run(d["q"].to(DEV), d["blocked_k"].to(DEV), d["block_table"].to(DEV), bad.to(DEV), 512, False, impl)
+    keep = [0, 2]
+    assert_out_close("out", out[keep], ref_out[keep])
+    assert_lse_close("lse", lse[keep], ref_lse[keep])
+    assert torch.isfinite(out[1].float()).all()
 
 
 def test_longcontext_shard_sample():

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 from oracle import sched_meta as osm
+from tests.helpers import check_schedule_properties
 
 pytestmark = pytest.mark.gpu
 
@@ -27,6 +28,22 @@ def _run_meta(b, P, bs, F, seqlens=None, topk=-1, extra_topk=0, topk_length=None
     return meta.cpu().numpy(), ns.cpu().numpy()
 
 
+def test_sched_meta_known_answers_on_the_gpu(golden_dir):
+    """The hand-derived vectors (dense, sparse with per-request lengths incl. 0, extra cache, zero-length requests,
+    more partitions than work, fixed overhead 3) against the CUDA kernel itself."""
+    import json
+    import os
+    for c in json.load(open(os.path.join(golden_dir, "sched_meta_known_answers.json")))["cases"]:
+        if "seqlens" in c:
+            meta, ns = _run_meta(len(c["seqlens"]), c["num_sm_parts"], c["block_size_n"], c["fixed_overhead"], seqlens=c["seqlens"])
+        else:
+            b = c.get("b") or len(c["topk_length"])
+            meta, ns = _run_meta(b, c["num_sm_parts"], c["block_size_n"], c["fixed_overhead"], topk=c["topk"], extra_topk=c["extra_topk"],
+                                 topk_length=c.get("topk_length"), extra_topk_length=c.get("extra_topk_length"))
+        assert meta[:, :7].tolist() == c["meta"], c
+        assert ns.tolist() == c["num_splits"], c
+
+
 def test_sched_meta_bit_exact_dense():
     rng = random.Random(0)
     cases = [([200, 70], 4), ([1000], 4), ([0], 3), ([0, 0, 5], 2), ([64] * 7, 74), ([8192] + [4096] * 127, 74)]
@@ -42,6 +59,7 @@ def test_sched_meta_bit_exact_dense():
             meta, ns = _run_meta(len(seq), P, 64, F, seqlens=seq)
             assert np.array_equal(meta[:, :7], ref_meta[:, :7]), (seq[:8], P, F)
             assert np.array_equal(ns, ref_ns), (seq[:8], P, F)
+            check_schedule_properties(meta, ns, seq, P, 64, F)        # the kernel's own output, not the oracle's
 
 
 def test_sched_meta_bit_exact_sparse():
@@ -57,6 +75,8 @@ def test_sched_meta_bit_exact_sparse():
         meta, ns = _run_meta(b, P, 64, 5, topk=topk, extra_topk=extra_topk, topk_length=tl, extra_topk_length=etl)
         assert np.array_equal(meta[:, :7], ref_meta[:, :7])
         assert np.array_equal(ns, ref_ns)
+        eff = osm.effective_seqlens(b, 64, None, topk, extra_topk, tl, etl)
+        check_schedule_properties(meta, ns, eff, P, 64, 5)
 
 
 def _combine_ref(lse_acc, o_acc, num_splits, b, s_q, h_q, sink, out_init, lse_init):
@@ -126,3 +146,22 @@ def test_combine_kernel(with_sink):
     assert torch.equal(lse_c == float("inf"), ref_lse == float("inf"))
     fin = torch.isfinite(ref_lse)
     assert torch.allclose(lse_c[fin], ref_lse[fin], rtol=1e-5, atol=1e-5)
+
+
+def test_uniform_partition_count_never_straddles_requests():
+    """mla_num_sm_parts_uniform returns either the general count or exactly the batch size; with the batch size every
+    partition holds exactly one whole request (the sparse decode path then skips the combine launch)."""
+    from flashmla_b200 import _capi
+    lib = _capi.lib()
+    general = lib.mla_num_sm_parts(0, _capi.MLA_MODE_SPARSE_DECODE, 128, 1, 1)
+    for b in (1, 7, 36, 37, 64, 73, 74, 75, 200):
+        for blocks in (1, 2, 8, 32, 33, 48):
+            P = lib.mla_num_sm_parts_uniform(0, _capi.MLA_MODE_SPARSE_DECODE, 128, 1, 1, b, blocks)
+            assert P in (b, general), (b, blocks, P)
+            if b > general:
+                assert P == general
+            if P == b:
+                meta, ns = _run_meta(b, P, 64, 5, topk=blocks * 64)
+                assert ns.tolist() == list(range(b + 1))
+                assert meta[:, 0].tolist() == list(range(b)) and meta[:, 1].tolist() == list(range(b))
+                assert not meta[:, 5].any() and not meta[:, 6].any()

@@ -93,24 +93,70 @@ def test_sparse_decode_all_invalid_and_unused_nan():
     assert (out[1] == 0).all() and (lse[1] == float("inf")).all()
 
 
-def test_sparse_decode_config3_sample():
+@pytest.mark.parametrize("s_kv,topk,page", [(512, 64, 2), (512, 64, 69), (1024, 576, 2), (1024, 576, 61), (2046, 2048, 576), (650, 576, 53)])
+@pytest.mark.parametrize("b,s_q", [(4, 1), (74, 3)])
+def test_sparse_decode_page_sizes(s_kv, topk, page, b, s_q):
+    """Page sizes other than 64, as the reference's grid has them (tests/test_flash_mla_sparse_decoding.py:37-57,
+    106-112): the kernel resolves index -> (index / page_size, index % page_size) itself, and a block's stride is not
+    page_size * 656 (one spare row per block)."""
+    from tests import workloads as W
+    d = W.sparse_decode_inputs(b, s_q, 128, s_kv, topk, seed=page + b, device="cpu", pad_rows=1, page_size=page)
+    assert d["kv_fp8"].shape[1] == page and d["kv_fp8"].stride(0) == (page + 1) * 656
+    kv_deq = quant.dequantize_v32(d["kv_fp8"])
+    attn_sink = torch.randn(128, generator=torch.Generator().manual_seed(7))
+    topk_length = torch.randint(0, topk + 1, (b,), generator=torch.Generator().manual_seed(8), dtype=torch.int32) if b == 4 else None
+    ref_out, ref_lse = attention.sparse_decode(d["q"], kv_deq, d["indices"], 576 ** -0.5, 512, attn_sink, topk_length)
+    out, lse = _decode(d["q"].to(DEV), d["kv_fp8"].to(DEV), d["indices"].to(DEV), 576 ** -0.5, attn_sink.to(DEV), _dev(topk_length))
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("page,extra_page", [(61, 2), (2, 69), (256, 64)])
+def test_sparse_decode_extra_cache_page_sizes(page, extra_page, impl):
+    """Main and extra cache with different page sizes (the extra one down to 2 tokens per page), per-request lengths
+    for both scopes, both kernel families."""
+    import flashmla_b200 as fm
+    from tests import workloads as W
+    b, s_q, h_q = 5, 2, 128
+    main = W.sparse_decode_inputs(b, s_q, h_q, 700, 192, seed=page, device="cpu", pad_rows=1, page_size=page)
+    extra = W.sparse_decode_inputs(b, s_q, h_q, 300, 128, seed=extra_page + 100, device="cpu", pad_rows=0, page_size=extra_page)
+    g = torch.Generator().manual_seed(9)
+    topk_length = torch.randint(0, 193, (b,), generator=g, dtype=torch.int32)
+    extra_topk_length = torch.randint(0, 129, (b,), generator=g, dtype=torch.int32)
+    attn_sink = torch.randn(h_q, generator=g)
+    ref_out, ref_lse = attention.sparse_decode(main["q"], quant.dequantize_v32(main["kv_fp8"]), main["indices"], 576 ** -0.5, 512,
+                                               attn_sink, topk_length, quant.dequantize_v32(extra["kv_fp8"]), extra["indices"],
+                                               extra_topk_length)
+    fm.set_impl(impl)
+    try:
+        out, lse = _decode(main["q"].to(DEV), main["kv_fp8"].to(DEV), main["indices"].to(DEV), 576 ** -0.5, attn_sink.to(DEV),
+                           topk_length.to(DEV), extra["kv_fp8"].to(DEV), extra["indices"].to(DEV), extra_topk_length.to(DEV))
+    finally:
+        fm.set_impl(0)
+    assert_out_close("out", out, ref_out)
+    assert_lse_close("lse", lse, ref_lse)
+
+
+def test_sparse_decode_config3_every_request():
     """batch 64, h_q 128, 32768 tokens per sequence, topk 2048 with the last 5% of each row -1, scale = amax/448:
-    the whole batch runs on the GPU, a sample of requests is checked against the oracle."""
+    the whole batch runs on the GPU and EVERY request is checked against the oracle (which de-quantises, request by
+    request, the 512 pages that request's block-table row owns)."""
     from tests import workloads as W
     d = W.sparse_decode_inputs(64, 1, 128, 32768, 2048, seed=0, device=DEV, data_on_device=True)
     out, lse = _decode(d["q"], d["kv_fp8"], d["indices"], 576 ** -0.5)
-    sample = [0, 31, 63]
-    idx = d["indices"][sample].cpu()
-    # de-quantise only the pages the sample touches (the oracle works on a compacted cache)
-    pages = torch.unique(idx[idx >= 0] // 64)
-    remap = torch.full((d["kv_fp8"].size(0),), -1, dtype=torch.int64)
-    remap[pages.long()] = torch.arange(pages.numel())
-    kv_small = quant.dequantize_v32(d["kv_fp8"][pages.to(DEV).long()].cpu().contiguous())
-    idx_small = torch.where(idx >= 0, (remap[(idx.clamp_min(0) // 64).long()] * 64 + idx % 64).to(torch.int32), idx)
-    ref_out, ref_lse = attention.sparse_decode(d["q"][sample].cpu(), kv_small, idx_small, 576 ** -0.5, 512)
-    assert_out_close("out", out[sample], ref_out)
-    assert_lse_close("lse", lse[sample], ref_lse)
-    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    out_c, lse_c, q_c, idx_c = out.cpu(), lse.cpu(), d["q"].cpu(), d["indices"].cpu()
+    for i in range(64):
+        idx = idx_c[i:i + 1]
+        pages = d["block_table"][i].long()                       # this request's pages, in sequence order
+        remap = torch.full((d["kv_fp8"].size(0),), -1, dtype=torch.int64)
+        remap[pages] = torch.arange(pages.numel())
+        kv_small = quant.dequantize_v32(d["kv_fp8"][pages.to(DEV)].cpu().contiguous())
+        idx_small = torch.where(idx >= 0, (remap[(idx.clamp_min(0) // 64).long()] * 64 + idx % 64).to(torch.int32), idx)
+        assert (idx_small[idx >= 0] >= 0).all()
+        ref_out, ref_lse = attention.sparse_decode(q_c[i:i + 1], kv_small, idx_small, 576 ** -0.5, 512)
+        assert_out_close(f"out[{i}]", out_c[i:i + 1], ref_out)
+        assert_lse_close(f"lse[{i}]", lse_c[i:i + 1], ref_lse)
 
 
 def _prefill(q, kv, indices, sm_scale, attn_sink=None, topk_length=None):
@@ -166,6 +212,24 @@ def test_sparse_prefill_config4_rows():
     assert_out_close("out", out, ref[0])
     assert_lse_close("max_logits", mx, ref[1])
     assert_lse_close("lse", lse, ref[2])
+
+
+def test_sparse_prefill_config4_full_size():
+    """The whole configuration (4096 query tokens, s_kv 32768, topk 2048) runs on the GPU; every 15th query token -
+    274 rows, which hit every CTA pair of the persistent grid (15 and the pair count are coprime) at every depth of
+    its stride - is checked against the oracle, the rest through size-independent properties."""
+    from tests import workloads as W
+    d = W.sparse_prefill_inputs(4096, 128, 32768, 2048, causal_base=28672, seed=0, device=DEV, data_on_device=True)
+    out, mx, lse = _prefill(d["q"], d["kv"], d["indices"], 576 ** -0.5)
+    rows = torch.arange(0, 4096, 15)
+    assert rows.numel() >= 256
+    ref = attention.sparse_prefill(d["q"][rows.to(DEV)].cpu(), d["kv"].cpu(), d["indices"][rows.to(DEV)].cpu(), 576 ** -0.5, 512, row_chunk=8)
+    assert_out_close("out", out[rows.to(DEV)], ref[0])
+    assert_lse_close("max_logits", mx[rows.to(DEV)], ref[1])
+    assert_lse_close("lse", lse[rows.to(DEV)], ref[2])
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all() and torch.isfinite(mx).all()
+    assert out.float().abs().max() <= d["kv"].float().abs().max()          # a convex combination of value rows
+    assert (lse >= mx - 1e-3).all()                                        # log-sum-exp is at least the maximum logit
 
 
 def test_fp8_cache_writer_bit_exact(golden_dir):

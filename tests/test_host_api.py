@@ -104,3 +104,18 @@ def test_api_mirrors_reference_misuse_checks():
     m.config = fm.FlashMLASchedMeta.Config(3, 1, 8, 64, 1, False, False, None, None, None)
     with pytest.raises(AssertionError, match="sched_meta.config.b must be equal to batch_size"):
         fm.flash_mla_with_kvcache(q, k, bt, sl, 512, m)
+
+
+def test_workspace_bytes():
+    """Host-only sizing of the split-KV scratch (no device is touched)."""
+    from flashmla_b200 import _capi
+    lib = _capi.lib()
+    off = ctypes.c_size_t(0)
+    total = lib.mla_workspace_bytes(128, 1, 128, 512, 74, ctypes.byref(off))
+    rows = (128 + 74) * 128
+    assert off.value == rows * 512 * 4 and off.value % 256 == 0
+    assert total == off.value + rows * 4
+    total = lib.mla_workspace_bytes(3, 2, 5, 512, 7, ctypes.byref(off))       # an odd row count: the LSE part stays 256-byte aligned
+    rows = (3 + 7) * 2 * 5
+    assert off.value >= rows * 512 * 4 and off.value % 256 == 0 and total == off.value + rows * 4
+    assert lib.mla_workspace_bytes(0, 1, 128, 512, 74, None) == 0 and b"positive" in lib.mla_last_error()

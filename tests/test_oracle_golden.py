@@ -1,7 +1,6 @@
 """Pins the CPU oracle (oracle/) against vectors produced by the reference's own
-torch code (tests/golden/make_golden.py) and against the hand-derived
-scheduler known answers."""
-import json
+torch code (tests/golden/make_golden.py).  The scheduler's known answers and properties:
+tests/test_sched_properties.py."""
 import os
 
 import numpy as np
@@ -18,15 +17,6 @@ BF16_ULP = 2.0 ** -7
 
 def _load(golden_dir, name):
     return torch.load(os.path.join(golden_dir, name), weights_only=False)
-
-
-def test_sched_meta_known_answers(golden_dir):
-    cases = json.load(open(os.path.join(golden_dir, "sched_meta_known_answers.json")))["cases"]
-    for c in cases:
-        meta, ns = sched_meta.get_sched_meta(len(c["seqlens"]), c["num_sm_parts"], c["block_size_n"],
-                                             c["fixed_overhead"], seqlens_k=c["seqlens"])
-        assert meta[:, :7].tolist() == c["meta"]
-        assert ns.tolist() == c["num_splits"]
 
 
 def test_dense_decode_oracle_matches_reference(golden_dir):

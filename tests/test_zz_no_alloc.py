@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run_pair(b, s_q, h_q, seqlens, seed):
+def _run_pair(b, s_q, h_q, seqlens, seed, check_oracle=False):
     import flashmla_b200 as fm
     from flashmla_b200 import _capi
     from tests import workloads as W
@@ -26,12 +26,13 @@ def _run_pair(b, s_q, h_q, seqlens, seed):
     # regular path through the public API (caller-side scratch)
     meta = fm.get_mla_metadata()[0]
     ref_out, ref_lse = fm.flash_mla_with_kvcache(q, kc, bt, sl, 512, meta, None, causal=True)
-    # allocation-free path through the C ABI: outputs and metadata are passed in, scratch is not
+    # allocation-free path through the C ABI: outputs, metadata and status words are passed in, scratch is not
     P = lib.mla_num_sm_parts(0, _capi.MLA_MODE_DENSE_DECODE, h_q, 1, s_q)
     assert (b + P) * s_q * h_q <= _capi.NOALLOC_MAX_ROWS
     sched, num_splits = _make_sched_meta(b, s_q, P, torch.device(DEV), seqlens_k=sl)
     out = torch.full((b, s_q, h_q, 512), float("nan"), dtype=torch.bfloat16, device=DEV)
     lse = torch.full((b, h_q, s_q), float("nan"), dtype=torch.float32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
     a = _capi.DenseDecodeArgs(
         b=b, s_q=s_q, h_q=h_q, h_kv=1, d_qk=576, d_v=512, num_blocks=kc.size(0), page_block_size=64,
         is_causal=int(s_q > 1), softmax_scale=576 ** -0.5,
@@ -41,23 +42,48 @@ def _run_pair(b, s_q, h_q, seqlens, seed):
         out=_capi.ptr(out), o_stride_b=out.stride(0), o_stride_s=out.stride(1), o_stride_h=out.stride(2),
         lse=_capi.ptr(lse), lse_stride_b=lse.stride(0), lse_stride_s=lse.stride(2), lse_stride_h=lse.stride(1),
         meta=_capi.ptr(sched), num_splits=_capi.ptr(num_splits), num_sm_parts=P,
-        lse_accum=None, o_accum=None, status=None, impl=0, stream=torch.cuda.current_stream().cuda_stream)
-    before = torch.cuda.memory_allocated()
+        lse_accum=None, o_accum=None, status=_capi.ptr(status), impl=0, dtype=_capi.MLA_DTYPE_BF16,
+        stream=torch.cuda.current_stream().cuda_stream)
+    _capi.check(lib.mla_dense_decode_noalloc(a), "mla_dense_decode_noalloc")    # (a device's first call also looks up the array's address)
+    torch.cuda.synchronize()
+    # a later call must not take device memory from anyone: neither from torch's allocator nor, unseen by it, from the
+    # driver (free device memory as the driver reports it stays where it was)
+    out.fill_(float("nan"))
+    lse.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated()
     _capi.check(lib.mla_dense_decode_noalloc(a), "mla_dense_decode_noalloc")
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes across the call"
+    assert torch.cuda.memory_allocated() == torch_before
+    assert status.tolist() == [0, 0, 0, 0], "a bounded wait ran out inside the allocation-free launch"
     fm.check_status()
     # same kernels, same schedule: identical up to nothing at all
     assert torch.equal(out.view(torch.int16), ref_out.view(torch.int16))
     assert torch.equal(lse, ref_lse)
+    if check_oracle:
+        from oracle import attention
+        from tests.helpers import assert_lse_close, assert_out_close
+        o_ref, l_ref = attention.dense_decode(q.cpu(), kc.cpu(), bt.cpu(), sl.cpu(), 512, True)
+        assert_out_close("out", out, o_ref)
+        assert_lse_close("lse", lse, l_ref)
     return out, lse
 
 
 def test_no_alloc_matches_regular_entry_point_twice():
     # the first call leaves partial results of a long, heavily split request in the shared scratch;
     # the second call (other lengths, other split pattern) must not be disturbed by them
-    _run_pair(3, 1, 128, [9000, 64, 300], seed=21)
-    _run_pair(4, 1, 128, [130, 5000, 1, 2049], seed=22)
+    _run_pair(3, 1, 128, [9000, 64, 300], seed=21, check_oracle=True)
+    _run_pair(4, 1, 128, [130, 5000, 1, 2049], seed=22, check_oracle=True)
+
+
+def test_no_alloc_admits_the_serving_shape():
+    """Batch 128 with 128 heads - (128 + 74) * 128 = 25856 rows of split scratch on a 148-SM part - fits the built-in array."""
+    from tests import workloads as W
+    seq = W.seqlens_normal(128, 512, 64, 1, 1024, True, seed=3).tolist()
+    _run_pair(128, 1, 128, seq, seed=23)
 
 
 def test_no_alloc_rejects_oversized_requests():

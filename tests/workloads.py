@@ -87,37 +87,37 @@ def dense_decode_inputs(cache_seqlens: torch.Tensor, s_q: int, h_q: int, h_kv: i
 
 def sparse_decode_inputs(b: int, s_q: int, h_q: int, s_kv: int, topk: int, pad_frac: float = 0.05, seed: int = 0,
                          device="cuda", pow2_scale: bool = False, pad_rows: int = 0,
-                         data_on_device: bool = False) -> Dict[str, torch.Tensor]:
-    """FP8 cache of s_kv tokens per request (656-byte records, scale = amax/448), random block table,
-    indices = unique tokens drawn without replacement, the last pad_frac of each row set to -1,
-    expressed as physical positions page*64 + offset."""
+                         data_on_device: bool = False, page_size: int = BLOCK) -> Dict[str, torch.Tensor]:
+    """FP8 cache of s_kv tokens per request (656-byte records, scale = amax/448) in pages of `page_size` tokens, random
+    block table, indices = unique tokens drawn without replacement, the last pad_frac of each row set to -1,
+    expressed as physical positions page * page_size + offset."""
     d = 576
-    blocks_per_seq = (s_kv + BLOCK - 1) // BLOCK
+    blocks_per_seq = (s_kv + page_size - 1) // page_size
     num_blocks = b * blocks_per_seq
     g = _gen(seed + 1)
     block_table = torch.randperm(num_blocks, generator=g).to(torch.int32).view(b, blocks_per_seq)
     if data_on_device:
         gd = _gen(seed + 2, device)
         q = torch.randn(b, s_q, h_q, d, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
-        kv_fp8 = torch.empty(num_blocks, BLOCK + pad_rows, 656, dtype=torch.float8_e4m3fn, device=device)[:, :BLOCK].unsqueeze(2)
-        step = 4096
+        kv_fp8 = torch.empty(num_blocks, page_size + pad_rows, 656, dtype=torch.float8_e4m3fn, device=device)[:, :page_size].unsqueeze(2)
+        step = max(1, 4096 * 64 // page_size)
         for i in range(0, num_blocks, step):
             n = min(step, num_blocks - i)
-            chunk = torch.randn(n, BLOCK, 1, d, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
+            chunk = torch.randn(n, page_size, 1, d, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
             kv_fp8[i:i + n] = quantize_fp8_kvcache(chunk, pow2_scale)
     else:
         q = torch.randn(b, s_q, h_q, d, generator=g).to(torch.bfloat16)
-        blocked_k = torch.randn(num_blocks, BLOCK, 1, d, generator=g).to(torch.bfloat16)
+        blocked_k = torch.randn(num_blocks, page_size, 1, d, generator=g).to(torch.bfloat16)
         kv_fp8 = quantize_fp8_kvcache(blocked_k, pow2_scale, pad_rows)
-    n_valid = topk - int(topk * pad_frac)
+    n_valid = min(topk - int(topk * pad_frac), s_kv)
     abs_idx = torch.full((b, s_q, topk), -1, dtype=torch.int64)
     for i in range(b):
         for t in range(s_q):
             abs_idx[i, t, :n_valid] = torch.randperm(s_kv, generator=g)[:n_valid]
     invalid = abs_idx < 0
     a = abs_idx.clamp_min(0)
-    page = torch.gather(block_table.long().unsqueeze(1).expand(b, s_q, blocks_per_seq), 2, a // BLOCK)
-    phys = (page * BLOCK + a % BLOCK)
+    page = torch.gather(block_table.long().unsqueeze(1).expand(b, s_q, blocks_per_seq), 2, a // page_size)
+    phys = (page * page_size + a % page_size)
     phys[invalid] = -1
     return dict(q=q.to(device), kv_fp8=kv_fp8.to(device) if not data_on_device else kv_fp8,
                 indices=phys.to(torch.int32).to(device), block_table=block_table, n_valid=n_valid)
