@@ -150,75 +150,86 @@ def make_host_buffers(w):
 
 
 class E2EPipeline:
-    """End-to-end steps through the public API with host buffers: every step copies its inputs from pinned host
-    memory to the device and reads its result back.  Consecutive steps are independent, so they are software-pipelined
-    over three streams (copy in / compute / copy out) with double-buffered device inputs and host outputs: the copy
-    engines of both directions and the SMs work at the same time, as in a serving loop that prepares the next batch
-    while the current one runs.  With compute=False only the copies run (the same bytes, no kernel): the ceiling the
-    host link sets for the end-to-end figure."""
+    """End-to-end passes through the public API with host buffers: every pass copies its inputs from pinned host memory
+    to the device, runs the API call (for dense decode including a new schedule: the sequence lengths are new) and
+    reads its result back into pinned host memory.  Consecutive passes are independent, so SLOTS of them are in flight
+    at once, each on its own stream with its own device input and host output buffers: the copy engines of both
+    directions and the SMs work at the same time, as in a serving loop that prepares the next batch while the current
+    one runs.  One pass per slot is captured in a CUDA graph (copies, schedule, kernels) so that the host thread's
+    per-call overhead stays off the clock; if capture is not possible the same sequence is issued call by call.
+    With compute=False only the copies run (the same bytes, no kernel): the ceiling the host link sets for this figure."""
+    SLOTS = 3
 
     def __init__(self, w, host, compute=True):
         self.w, self.host, self.compute = w, host, compute
         dev = w["inputs"]["q"].device
-        self.s_in, self.s_cmp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.streams = [torch.cuda.Stream(dev) for _ in range(self.SLOTS)]
         self.keys = [k for k in host if k not in ("out", "lse")]
-        self.dev_in = [{k: torch.empty_like(host[k], device=dev) for k in self.keys} for _ in range(2)]
-        self.host_out = [{k: torch.empty_like(host[k]).pin_memory() for k in ("out", "lse")} for _ in range(2)]
-        self.dev_out = None
-        if not compute:
-            self.dev_out = {k: torch.empty_like(host[k], device=dev) for k in ("out", "lse")}
-        self.cmp_done = [None, None]
-        self.out_done = [None, None]
-        self.keep = [None, None]
+        self.dev_in = [{k: torch.empty_like(host[k], device=dev) for k in self.keys} for _ in range(self.SLOTS)]
+        self.host_out = [{k: torch.empty_like(host[k]).pin_memory() for k in ("out", "lse")} for _ in range(self.SLOTS)]
+        self.dev_out = {k: torch.empty_like(host[k], device=dev) for k in ("out", "lse")} if not compute else None
+        self.done = [None] * self.SLOTS
+        self.keep = [None] * self.SLOTS
+        self.graphs = None
+        self.mode = "call by call"
+        try:
+            graphs = []
+            for slot in range(self.SLOTS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self.streams[slot]):
+                    self.keep[slot] = self._one_pass(slot)
+                graphs.append(g)
+            self.graphs = graphs
+            self.mode = "one CUDA graph per slot (copies + schedule + kernels)"
+        except Exception as exc:
+            print(f"bench.py: end-to-end leg issued call by call ({exc})", file=sys.stderr)
+            torch.cuda.synchronize()
+
+    def _one_pass(self, slot):
+        """host -> device, API call, device -> host; on the current stream."""
+        import flashmla_b200 as fm
+        w, d, x = self.w, self.w["inputs"], self.dev_in[slot]
+        for k in self.keys:
+            x[k].copy_(self.host[k], non_blocking=True)
+        if not self.compute:
+            out, lse = self.dev_out["out"], self.dev_out["lse"]
+        elif w["kind"] == "dense":
+            meta, _ = fm.get_mla_metadata()                    # the sequence lengths are new: the schedule is recomputed
+            out, lse = fm.flash_mla_with_kvcache(x["q"], d["blocked_k"], x["block_table"], x["cache_seqlens"], D_V, meta,
+                                                 None, D_QK ** -0.5, True)
+        elif w["kind"] == "sparse_decode":
+            out, lse = fm.flash_mla_with_kvcache(x["q"], d["kv_fp8"], None, None, D_V, w["meta"], None, D_QK ** -0.5,
+                                                 False, True, x["indices"])
+        else:
+            out, _, lse = fm.flash_mla_sparse_fwd(x["q"], d["kv"], x["indices"], D_QK ** -0.5)
+        self.host_out[slot]["out"].copy_(out, non_blocking=True)
+        self.host_out[slot]["lse"].copy_(lse, non_blocking=True)
+        return out, lse
 
     def step(self, i):
-        import flashmla_b200 as fm
-        w, d, slot = self.w, self.w["inputs"], i & 1
-        with torch.cuda.stream(self.s_in):
-            if self.cmp_done[slot] is not None:
-                self.s_in.wait_event(self.cmp_done[slot])          # the device input buffers of step i-2 have been read
-            for k in self.keys:
-                self.dev_in[slot][k].copy_(self.host[k], non_blocking=True)
-            in_done = torch.cuda.Event()
-            in_done.record(self.s_in)
-        with torch.cuda.stream(self.s_cmp):
-            self.s_cmp.wait_event(in_done)
-            x = self.dev_in[slot]
-            if not self.compute:
-                out, lse = self.dev_out["out"], self.dev_out["lse"]
-            elif w["kind"] == "dense":
-                meta, _ = fm.get_mla_metadata()                    # the sequence lengths are new: the schedule is recomputed
-                out, lse = fm.flash_mla_with_kvcache(x["q"], d["blocked_k"], x["block_table"], x["cache_seqlens"], D_V, meta,
-                                                     None, D_QK ** -0.5, True)
-            elif w["kind"] == "sparse_decode":
-                out, lse = fm.flash_mla_with_kvcache(x["q"], d["kv_fp8"], None, None, D_V, w["meta"], None, D_QK ** -0.5,
-                                                     False, True, x["indices"])
+        slot = i % self.SLOTS
+        if self.done[slot] is not None:
+            self.done[slot].synchronize()          # the host has the result of pass i - SLOTS before its buffers are reused
+        with torch.cuda.stream(self.streams[slot]):
+            if self.graphs is not None:
+                self.graphs[slot].replay()
             else:
-                out, _, lse = fm.flash_mla_sparse_fwd(x["q"], d["kv"], x["indices"], D_QK ** -0.5)
-            self.cmp_done[slot] = torch.cuda.Event()
-            self.cmp_done[slot].record(self.s_cmp)
-        with torch.cuda.stream(self.s_out):
-            self.s_out.wait_event(self.cmp_done[slot])
-            if self.out_done[slot] is not None:
-                self.out_done[slot].synchronize()                  # the host reads the result of step i-2 before it is overwritten
-            self.host_out[slot]["out"].copy_(out, non_blocking=True)
-            self.host_out[slot]["lse"].copy_(lse, non_blocking=True)
-            self.out_done[slot] = torch.cuda.Event()
-            self.out_done[slot].record(self.s_out)
-        self.keep[slot] = (out, lse)                               # outputs stay referenced until their copy is two steps old
+                self.keep[slot] = self._one_pass(slot)
+            self.done[slot] = torch.cuda.Event()
+            self.done[slot].record()
 
     def run(self, steps):
         cur = torch.cuda.current_stream()
-        for st in (self.s_in, self.s_cmp, self.s_out):
+        for st in self.streams:
             st.wait_stream(cur)
         for i in range(steps):
             self.step(i)
-        for st in (self.s_in, self.s_cmp, self.s_out):
+        for st in self.streams:
             cur.wait_stream(st)
 
     def timed(self, steps, reps, barrier):
         """K steps, each `reps` pipelined passes between one event pair; returns the mean milliseconds per pass."""
-        self.run(3)
+        self.run(2 * self.SLOTS)
         barrier()
         total = 0.0
         for _ in range(steps):
@@ -642,7 +653,7 @@ def main():
     ms_e2e = pipe.timed(args.steps, reps_e2e, barrier)
     out_chk, lse_chk = run_step(w)                                  # the pipelined path returns the same result
     torch.cuda.synchronize()
-    last = pipe.host_out[(reps_e2e - 1) & 1]
+    last = pipe.host_out[(reps_e2e - 1) % pipe.SLOTS]
     if not (torch.equal(last["out"].view(torch.int16), out_chk.cpu().view(torch.int16)) and torch.equal(last["lse"], lse_chk.cpu())):
         raise SystemExit("bench.py: the end-to-end leg returned a different result than the device-resident leg")
     ms_copy = E2EPipeline(w, host, compute=False).timed(max(3, args.steps // 2), reps_e2e, barrier)
@@ -674,7 +685,7 @@ def main():
     clk = clocks.summary()
     e2e = {"value": units_all / (ms_e2e_all / 1e3), "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
            "ms_per_step": ms_e2e_all, "replays_per_step": reps_e2e,
-           "pipelining": "passes overlapped on 3 streams (copy in / compute / copy out), double-buffered",
+           "pipelining": f"{E2EPipeline.SLOTS} passes in flight, each on its own stream with its own buffers; {pipe.mode}",
            "host_binding": numa,
            "copy_only": {"ms_per_step": ms_copy_all, "per_rank_gbs": (h2d + d2h) / 1e9 / (ms_copy_all / 1e3),
                          "aggregate_gbs": world * (h2d + d2h) / 1e9 / (ms_copy_all / 1e3),

@@ -448,7 +448,14 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
     using WaiterT = Waiter<DENSE>;
     const uint32_t peer_flag = map_to_cta(smem_addr(&sm.aborted), cta_rank ^ 1u);
-    WaiterT wt(p.status, &sm.aborted, peer_flag, p.wait_limit, !DENSE && warp < 12, MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : 0u);
+#ifndef MLA_DENSE_PARK_WARPS
+#define MLA_DENSE_PARK_WARPS 99          // dense mode: warps from this index on park between barrier probes
+#endif
+#ifndef MLA_DENSE_PARK_SLEEP
+#define MLA_DENSE_PARK_SLEEP 0u
+#endif
+    WaiterT wt(p.status, &sm.aborted, peer_flag, p.wait_limit, DENSE ? warp >= MLA_DENSE_PARK_WARPS : warp < 12,
+               MODE == MODE_SPARSE_DECODE ? MLA_SLEEP_NS : (DENSE ? MLA_DENSE_PARK_SLEEP : 0u));
     const int oob_page = p.num_blocks;                     // a page coordinate outside the cache: TMA fills zeros
     // what the wind-down has to wait for after an expired wait (thread 0: ring fills and Q boxes it armed)
     uint32_t fills_armed = 0, q_armed = 0;
