@@ -87,22 +87,28 @@ enum { MODE_DENSE = 0, MODE_PREFILL = 1, MODE_SPARSE_DECODE = 2 };
 template <int MODE>
 struct Lay {
     static constexpr bool DENSE = MODE == MODE_DENSE;
-    static constexpr int NKS = DENSE ? 4 : 3;             // K ring slots; group j of tile g uses slot (3 g + j) mod NKS
-    static constexpr int S_BUFS = DENSE ? 1 : 2;          // S accumulators in tensor memory
-    static constexpr int Q_TMEM_CHUNKS = DENSE ? 9 : 7;   // 64-dim chunks of Q kept in tensor memory (the rest in SC_Q78)
-    static constexpr int Q_SPLIT = DENSE ? 5 : 4;         // chunks [0, Q_SPLIT) are moved there by softmax warpgroup 0, the others by 1
+    // WIDE plan (dense decode): all 576 dims of Q in tensor memory (288 columns) next to ONE S accumulator, which frees
+    // the shared memory for a K ring of FOUR groups.  The gather modes keep the narrow plan (dims 0..447 of Q in tensor
+    // memory, 448..575 in shared memory, two S accumulators, three groups): prefill is paced by the copy instructions of
+    // its gather warps, not by the ring (measured with the wide plan: 3.49 against 3.41 ms), and FP8 decode needs 4 KB for
+    // the tokens' scales.
+    static constexpr bool WIDE = MODE == MODE_DENSE;
+    static constexpr int NKS = WIDE ? 4 : 3;              // K ring slots; group j of tile g is fill 3 g + j and uses slot (3 g + j) mod NKS
+    static constexpr int S_BUFS = WIDE ? 1 : 2;           // S accumulators in tensor memory
+    static constexpr int Q_TMEM_CHUNKS = WIDE ? 9 : 7;    // 64-dim chunks of Q kept in tensor memory (the rest in SC_Q78)
+    static constexpr int Q_SPLIT = WIDE ? 5 : 4;          // chunks [0, Q_SPLIT) are moved there by softmax warpgroup 0, the others by 1
     static constexpr uint32_t TM_S = 0, TM_Q = 128 * S_BUFS;
-    static constexpr int SC_Q78 = 0;                                    // gather modes: Q dims 448..575, 2 x [128][64]
-    static constexpr int SC_KRING = DENSE ? 0 : 2 * 16384;
+    static constexpr int SC_Q78 = 0;                                    // narrow plan: Q dims 448..575, 2 x [128][64]
+    static constexpr int SC_KRING = WIDE ? 0 : 2 * 16384;
     static constexpr int SC_STAGE = SC_KRING + NKS * K_GROUP_BYTES;     // 8 warps x 4 KB P staging
     static constexpr int SC_SIDE = SC_STAGE + 8 * 4096;                 // 4 warps x 144 B factor/flag staging
     static constexpr int SC_XMAX = SC_SIDE + 4 * SIDE_BYTES;            // [2][2][128] floats
     static constexpr int SC_END = SC_XMAX + 2 * 2 * ROWS * 4;
     // gather modes only
     static constexpr int SC_MASK = SC_END;                // validity bits of the last 4 tiles, [4][4] words
-    static constexpr int SC_LSUM = SC_MASK + 64;          // row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
+    static constexpr int SC_LSUM = SC_MASK + 64;          // narrow plan: row sums of softmax warpgroup 1, handed to warpgroup 0 at the end of a request
     static constexpr int SC_SCALES = SC_LSUM + ROWS * 4;  // FP8 decode: the 4 scales of every token of the last two tiles, [2][128] float4
-    static constexpr int SC_TOTAL = DENSE ? SC_END : SC_SCALES + 2 * ROWS * 16;
+    static constexpr int SC_TOTAL = DENSE ? SC_END : (WIDE ? SC_MASK + 64 : SC_SCALES + 2 * ROWS * 16);
     static_assert(TM_Q + Q_TMEM_CHUNKS * 32 <= 512, "tensor-memory columns of the score CTA");
 };
 // value CTA (all modes)
@@ -356,10 +362,9 @@ __device__ __noinline__ void zero_v_rows(uint8_t* vst, int first) {
 template <int MODE>
 __device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qrow, bool row_ok, int half, int r, uint32_t tlane) {
     using L = Lay<MODE>;
-    constexpr bool DENSE = MODE == MODE_DENSE;
-    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT, c_smem = half ? 8 : 7;
+    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? L::Q_TMEM_CHUNKS : L::Q_SPLIT, c_smem = half ? 8 : 7;
 #pragma unroll 1
-    for (int c = c_begin; c < c_end + (DENSE ? 0 : 1); ++c) {
+    for (int c = c_begin; c < c_end + (L::WIDE ? 0 : 1); ++c) {
         const int chunk = c < c_end ? c : c_smem;
         uint32_t v[32];
         if (row_ok) {
@@ -490,16 +495,16 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         if (!DENSE) {
             // sparse modes: the gather warpgroup fills the rings
             if (p.q_tma && cta_rank == 0 && lane == 0) {
-                uint32_t g = 0, nreq = 0;
+                uint32_t ks = 0, nreq = 0;
                 for (WalkerT wk(p, part); wk.valid(); wk.next(), ++nreq) {
                     const Work w = wk.get();
                     issue_q(w);
                     WAIT_OR_LEAVE(wt, false, &sm.ring_released, nreq & 1, 11);     // (a request without tiles must not be overtaken)
                     // The next request's boxes may go out once every MMA of this one has finished with the ring and with
-                    // chunks 7, 8 of Q.  A parity wait only means what it says to a thread that has seen every earlier
-                    // phase of the barrier, so this thread follows the ring tile by tile.
-                    for (int i = 0; i < w.ntiles; ++i, ++g)
-                        for (int grp = 0; grp < 3; ++grp) WAIT_OR_LEAVE(wt, false, &sm.kv_empty[grp], g & 1, 13);
+                    // Q.  A parity wait only means what it says to a thread that has seen every earlier phase of the
+                    // barrier, so this thread follows the ring fill by fill.
+                    for (int i = 0; i < 3 * w.ntiles; ++i, ++ks)
+                        WAIT_OR_LEAVE(wt, false, &sm.kv_empty[ks % NKS], (ks / NKS) & 1, 13);
                 }
             }
         } else if (lane == 0) {
@@ -591,17 +596,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         // The probe of the next group's barrier is issued before this group's MMAs so that its
                         // latency hides behind them (the MMA queue is shallow: time the issuing thread spends
                         // waiting is time the tensor pipe idles).
-                        // (gather modes: three slots, so group j of every tile sits in slot j with the tile's parity and
+                        // (narrow plan: three slots, so group j of every tile sits in slot j with the tile's parity and
                         // every address below is a compile-time offset)
-                        if (!DENSE) { slot = 0; par = g & 1; }
+                        if (!L::WIDE) { slot = 0; par = g & 1; }
                         bool ready = mbar_try_wait(kv_full0 + slot * 8, par);
 #pragma unroll
                         for (int grp = 0; grp < 3; ++grp) {
-                            const uint32_t cur = DENSE ? slot : (uint32_t)grp;
+                            const uint32_t cur = L::WIDE ? slot : (uint32_t)grp;
                             if (!ready) WAIT_OR_LEAVE(wt, false, &sm.kv_full[cur], par, 3);
                             tc_fence_after();
-                            if (DENSE) { if (++slot == (uint32_t)NKS) { slot = 0; par ^= 1; } }
-                            if (grp < 2) ready = mbar_try_wait(kv_full0 + (DENSE ? slot : (uint32_t)(grp + 1)) * 8, par);
+                            if (L::WIDE) { if (++slot == (uint32_t)NKS) { slot = 0; par ^= 1; } }
+                            if (grp < 2) ready = mbar_try_wait(kv_full0 + (L::WIDE ? slot : (uint32_t)(grp + 1)) * 8, par);
                             const uint32_t grp_lo = kring_lo + cur * (K_GROUP_BYTES >> 4);
 #pragma unroll
                             for (int c = 0; c < 3; ++c) {
@@ -856,14 +861,18 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     // 16 bytes) is copied by two full-warp instructions (chunks 0-3, chunks 4-7) and the RoPE chunk of
                     // four rows by a third: 72 instructions per 32 rows.  The ring barriers still count per group of 3
                     // chunks: every group's arrival is issued once all copies that touch it have been issued.
-                    const uint32_t par = ((ks / NKS) & 1) ^ 1;
+                    // the tile's three groups are fills ks, ks + 1, ks + 2 of the ring; chunk c of the tile lives in the slot of
+                    // group c / 3, at chunk position c % 3
                     const uint32_t ring0 = smem_addr(sm.data + L::SC_KRING) + gw * 32 * 128;
+                    // (three slots: group j sits in slot j and every address below is a compile-time offset)
+                    const uint32_t slot0 = L::WIDE ? ks % NKS : 0u, slot1 = L::WIDE ? (ks + 1) % NKS : 1u, slot2 = L::WIDE ? (ks + 2) % NKS : 2u;
                     const int c = lane & 7;
                     if (ring_lent) { WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_p & 1, 211); ring_lent = false; }
-                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[0], par, 201);
-                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[1], par, 201);
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[slot0], ((ks / NKS) & 1) ^ 1, 201);
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[slot1], (((ks + 1) / NKS) & 1) ^ 1, 201);
                     {
-                        const uint32_t dst0 = ring0 + (lane >> 3) * K_CHUNK_BYTES;
+                        const int ch = lane >> 3;                     // chunks 0-3: 0, 1, 2 in group 0, chunk 3 in group 1
+                        const uint32_t dst0 = ring0 + (ch < 3 ? slot0 * K_GROUP_BYTES + ch * K_CHUNK_BYTES : slot1 * K_GROUP_BYTES);
 #pragma unroll 8
                         for (int rr = 0; rr < 32; ++rr) {
                             const int rid = __shfl_sync(0xffffffffu, row_id, rr);
@@ -871,10 +880,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
                         }
                     }
-                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[0]));
-                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[2], par, 201);
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot0]));
+                    WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[slot2], (((ks + 2) / NKS) & 1) ^ 1, 201);
                     {
-                        const uint32_t dst0 = ring0 + (4 + (lane >> 3)) * K_CHUNK_BYTES;
+                        const int ch = 4 + (lane >> 3);               // chunks 4-7: 4, 5 in group 1, chunks 6, 7 in group 2
+                        const uint32_t dst0 = ring0 + (ch < 6 ? slot1 * K_GROUP_BYTES + (ch - 3) * K_CHUNK_BYTES
+                                                              : slot2 * K_GROUP_BYTES + (ch - 6) * K_CHUNK_BYTES);
 #pragma unroll 8
                         for (int rr = 0; rr < 32; ++rr) {
                             const int rid = __shfl_sync(0xffffffffu, row_id, rr);
@@ -882,9 +893,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
                         }
                     }
-                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[1]));
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot1]));
                     {
-                        const uint32_t dst0 = ring0 + 8 * K_CHUNK_BYTES;
+                        const uint32_t dst0 = ring0 + slot2 * K_GROUP_BYTES + 2 * K_CHUNK_BYTES;      // chunk 8
 #pragma unroll
                         for (int q4 = 0; q4 < 8; ++q4) {
                             const int rr = 4 * q4 + (lane >> 3);
@@ -893,7 +904,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
                         }
                     }
-                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[2]));
+                    cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot2]));
                     ks += 3;
                 } else {
                     // warp gw owns tokens 16*gw .. 16*gw+15 of each page; one instruction copies 512 bytes of one row
@@ -987,7 +998,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const __nv_bfloat16* qrow = MODE == MODE_PREFILL
                         ? p.q + (int64_t)w.req * p.q_ss + (int64_t)hd * p.q_sh
                         : p.q + (int64_t)w.req * p.q_sb + (int64_t)t * p.q_ss + (int64_t)hd * p.q_sh;
-                    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? 7 + 2 * (int)DENSE : L::Q_SPLIT;
+                    const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? L::Q_TMEM_CHUNKS : L::Q_SPLIT;
                     if (p.q_tma) {
                         // Q arrived as TMA boxes: in the gather modes chunks 7 and 8 are in place; the others wait in the K
                         // ring as [row][128 B] with the 128-byte swizzle
@@ -1105,10 +1116,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     }
                 }
                 // final statistics of this request for the epilogue in the value CTA: warpgroup 1 hands its row sums to
-                // warpgroup 0, which sends sum, running maximum and true maximum.  (Dense mode has no spare shared memory:
+                // warpgroup 0, which sends sum, running maximum and true maximum.  (The wide plan has no spare shared memory:
                 // the hand-over uses the row-maximum slots of the tile parity that is not in use.)
                 {
-                    float* lsum = DENSE ? xmax + ((g & 1) * 2) * ROWS : reinterpret_cast<float*>(sm.data + L::SC_LSUM);
+                    float* lsum = L::WIDE ? xmax + ((g & 1) * 2) * ROWS : reinterpret_cast<float*>(sm.data + L::SC_LSUM);
                     if (half == 1) lsum[r] = l_run;
                     BAR_OR_LEAVE(wt.aborted);
                     if (half == 0) l_run += lsum[r];
