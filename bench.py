@@ -600,6 +600,7 @@ def main():
     # the API neither allocates outside torch's allocator nor synchronises, so it can be captured) ----------------------
     ms_step, launch_mode = ms_eager, "eager launches"
     ms_cold = None
+    kernel_ms_isolated = None
     g_out = g_lse = None
     try:
         eager_out, eager_lse = run_step(w)
@@ -634,6 +635,16 @@ def main():
             torch.cuda.synchronize()
             total += e0.elapsed_time(e1)
         ms_cold = total / args.steps
+        # ... and every kernel of an isolated, cold-L2 pass on its own (eager launches with an event pair around each):
+        # what the kernels take when the part is not yet held back by its power limit
+        timer_iso = KernelTimer()
+        for _ in range(args.steps):
+            scrub.fill_(1)
+            fmi.set_kernel_timer(timer_iso)
+            run_step(w)
+            fmi.set_kernel_timer(None)
+            torch.cuda.synchronize()
+        kernel_ms_isolated = timer_iso.mean_ms()
         del scrub
     except Exception as exc:                      # capture is an optimisation of the launch path, never a requirement
         print(f"bench.py: CUDA graph capture not used ({exc})", file=sys.stderr)
@@ -675,6 +686,16 @@ def main():
     else:
         roof = {"bound": "tensor", "achieved": w["flops"] / 1e12 / (k_ms / 1e3), "peak": peaks["tflops"], "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
+    roof["timed"] = "inside the timed region: back-to-back passes, clocks as sampled (see clocks)"
+    if kernel_ms_isolated is not None:
+        # the same kernel launched alone after an L2 scrub (burst clocks): comparable with the burst peak figures
+        k_iso = kernel_ms_isolated[main_kernel]
+        ach = (w["bytes"] / 1e9 if w["kind"] == "dense" else w["flops"] / 1e12) / (k_iso / 1e3)
+        roof["isolated"] = {"kernel_ms": k_iso, "achieved": ach, "frac": ach / roof["peak"]}
+    if w["kind"] == "dense":
+        # dense decode with 128 heads sits at the ridge: its arithmetic intensity is about 242 FLOP per cache byte, so the
+        # tensor pipe's SUSTAINED peak (power-capped) bounds it at nearly the same point as the HBM peak does
+        roof["tensor_frac_of_sustained_peak"] = (w["flops"] / 1e12 / (k_ms / 1e3)) / peaks["tflops_sustained"]
     traffic, traffic_commit = captured_traffic(args.workload) if world == 1 else (None, None)
     roof["traffic"] = traffic
     roof["traffic_captured_at_commit"] = traffic_commit
@@ -705,7 +726,8 @@ def main():
         "ms_x_sm_ghz": ms_step_all * clk["sm_mhz"] / 1e3 if clk["sm_mhz"] else None,
         "tflops": flops_all / 1e12 / (ms_step_all / 1e3), "hbm_gbs": bytes_all / 1e9 / (ms_step_all / 1e3),
         "kv_tokens_per_s": tokens_all / (ms_step_all / 1e3),
-        "kernel_ms": kernel_ms, "gpu_launches": launches_per_pass * reps * args.steps,
+        "kernel_ms": kernel_ms, "kernel_ms_isolated_cold_l2": kernel_ms_isolated,
+        "gpu_launches": launches_per_pass * reps * args.steps,
         "roofline": roof, "clocks": clk, "e2e": e2e,
     }
     if "flops_padded" in w:

@@ -448,6 +448,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     __syncthreads();
     tc_fence_after();
     cluster_sync();                                        // the peer's barriers exist before anyone arrives remotely
+    // Programmatic dependent launch: everything above ran while the previous kernel of the stream (the tile scheduler,
+    // or whatever produced q) was still draining; from here on its results are read.  The kernel after this one (the
+    // split-KV combine) may be scheduled as SMs become free: it waits for this grid's completion itself.
+    griddep_wait();
+    griddep_launch_dependents();
     const uint32_t tmem = sm.tmem_base;
     // gather modes: the gather warps need the issue slots that waiting warps would otherwise spin on
     // (FP8 decode, where a tile takes several microseconds, also sleeps between probes)
@@ -1528,11 +1533,11 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
     if (fp16) {
         static bool configured[64] = {};
         if (int rc = configure_once(attn_sm100_kernel<MODE_DENSE, true>, configured)) return rc;
-        attn_sm100_kernel<MODE_DENSE, true><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(cm.kmap, cm.vmap, qmap, p);
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_DENSE, true>, grid, dim3(NTHREADS), sizeof(Smem), (cudaStream_t)a.stream, cm.kmap, cm.vmap, qmap, p));
     } else {
         static bool configured[64] = {};
         if (int rc = configure_once(attn_sm100_kernel<MODE_DENSE, false>, configured)) return rc;
-        attn_sm100_kernel<MODE_DENSE, false><<<grid, NTHREADS, sizeof(Smem), (cudaStream_t)a.stream>>>(cm.kmap, cm.vmap, qmap, p);
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_DENSE, false>, grid, dim3(NTHREADS), sizeof(Smem), (cudaStream_t)a.stream, cm.kmap, cm.vmap, qmap, p));
     }
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
@@ -1575,7 +1580,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, 1, a.s_q, a.h_q, 0, a.q_stride_s, a.q_stride_h, a.h_q < ROWS ? a.h_q : ROWS, 1,
                            &p.q_box_bytes) ? 1 : 0;
-    attn_sm100_kernel<MODE_PREFILL, false><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(kmap, kmap, qmap, p);
+    MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_PREFILL, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, kmap, kmap, qmap, p));
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1618,7 +1623,7 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h,
                            a.h_q < ROWS ? a.h_q : ROWS, 1, &p.q_box_bytes) ? 1 : 0;
     dim3 grid(2, a.s_q, a.num_sm_parts);
-    attn_sm100_kernel<MODE_SPARSE_DECODE, false><<<grid, NTHREADS_GATHER, sizeof(Smem), (cudaStream_t)a.stream>>>(unused_map, unused_map, qmap, p);
+    MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, unused_map, unused_map, qmap, p));
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

@@ -18,6 +18,8 @@ constexpr int COMBINE_WARPS = 8;
 
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 combine_kernel(const mla_combine_args_t a) {
+    // launched with programmatic stream serialization: the decode kernel before it may still be running
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int bs_idx = blockIdx.x;                       // request * s_q + query token
     const int req = bs_idx / a.s_q, t = bs_idx - req * a.s_q;
@@ -95,8 +97,7 @@ int launch_combine(const mla_combine_args_t& a) {
     MLA_CHECK_ARG(((uintptr_t)a.out & 7u) == 0 && a.o_stride_b % 4 == 0 && a.o_stride_s % 4 == 0 && a.o_stride_h % 4 == 0,
                   "combine: out must be 8-byte aligned with strides that are multiples of 4 elements");
     dim3 grid(a.b * a.s_q, (a.h_q + COMBINE_WARPS - 1) / COMBINE_WARPS);
-    combine_kernel<<<grid, COMBINE_WARPS * 32, 0, (cudaStream_t)a.stream>>>(a);
-    MLA_CHECK_CUDA(cudaGetLastError());
+    MLA_CHECK_CUDA(launch_dependent(combine_kernel, grid, dim3(COMBINE_WARPS * 32), 0, (cudaStream_t)a.stream, a));
     return MLA_OK;
 }
 

@@ -51,6 +51,20 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a);
 int launch_quantize_fp8(const mla_quantize_args_t& a);
 int launch_bounded_wait_selftest(long long limit_cycles, int code, int* status, int* flag_out, void* stream);
 
+// Launch with programmatic stream serialization: the kernel may begin (prologue only - it must call
+// griddepcontrol.wait before it touches memory the previous kernel of the stream writes) while that kernel drains.
+// The reference chains its decode and combine kernels the same way (csrc/smxx/decode/combine/combine.cu:198-210).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 

@@ -18,6 +18,9 @@ namespace mla {
 
 __global__ void __launch_bounds__(128, 1)
 sched_meta_kernel(const mla_sched_meta_args_t a) {
+    // the decode kernel that follows is launched with programmatic stream serialization: let its prologue (barrier and
+    // tensor-memory set-up) start now; it waits for this kernel's completion before it reads the metadata
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ int smem_i[];
     int* nblk_s = smem_i;                // [b]  KV blocks of every request; -1 marks a zero-length request (1 block)
     int* nsplit_s = smem_i + a.b;        // [b + 1]

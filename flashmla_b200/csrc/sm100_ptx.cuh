@@ -159,6 +159,13 @@ __device__ __forceinline__ void st_global_v8(void* ptr, uint32_t a0, uint32_t a1
                  ::"l"(ptr), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7) : "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running; griddep_wait() blocks until that kernel has completed and its memory is visible (a no-op
+// for a plain launch).  griddep_launch_dependents() lets the NEXT kernel of the stream start launching early.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- proxies / fences ------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
