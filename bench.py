@@ -496,13 +496,41 @@ def metric_of(w):
     return "mla_dense_decode_hbm_gbs", "GB/s", w["bytes"] / 1e9
 
 
+def bench_quantize(args):
+    """The cache-write kernel (bf16 token rows -> 656-byte FP8 records) on 32768 blocks of 64 random rows: a side
+    measurement of the step before sparse decode, one JSON line of its own."""
+    from flashmla_b200.kvcache import quantize_fp8_kvcache, BYTES_PER_TOKEN
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    blocks = 32768
+    x = torch.randn(blocks, 64, 1, D_QK, device="cuda", dtype=torch.bfloat16)
+    for _ in range(max(args.warmup, 3)):
+        quantize_fp8_kvcache(x)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.steps):
+        quantize_fp8_kvcache(x)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    ntok = blocks * 64
+    peaks = measured_peaks()
+    gbs = ntok * (2 * D_QK + BYTES_PER_TOKEN) / ms / 1e6
+    print(json.dumps({"metric": "mla_quantize_fp8_kvcache_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16->e4m3", "data": "synthetic",
+                      "config": {"workload": f"FP8 cache writer, {ntok} tokens of 576 bf16 -> 656-byte records (read + written bytes, > L2)"},
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": gbs / peaks["hbm"],
+                                   "traffic": None, "peak_source": peaks["source"]}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill", "quantize"])
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--replays", type=int, default=0, help="passes per timed step (0: as many as make a step last about 20 ms)")
@@ -514,6 +542,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.workload == "quantize":
+        bench_quantize(args)
+        return
     if args.impl == "reference":
         if rank != 0:
             return
