@@ -497,12 +497,12 @@ def metric_of(w):
 
 
 def bench_quantize(args):
-    """The cache-write kernel (bf16 token rows -> 656-byte FP8 records) on 32768 blocks of 64 random rows: a side
+    """The cache-write kernel (bf16 token rows -> 656-byte FP8 records) on --quant-blocks (default 32768) blocks of 64 random rows: a side
     measurement of the step before sparse decode, one JSON line of its own."""
     from flashmla_b200.kvcache import quantize_fp8_kvcache, BYTES_PER_TOKEN
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
-    blocks = 32768
+    blocks = args.quant_blocks
     x = torch.randn(blocks, 64, 1, D_QK, device="cuda", dtype=torch.bfloat16)
     for _ in range(max(args.warmup, 3)):
         quantize_fp8_kvcache(x)
@@ -534,6 +534,7 @@ def main():
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--replays", type=int, default=0, help="passes per timed step (0: as many as make a step last about 20 ms)")
+    ap.add_argument("--quant-blocks", type=int, default=32768, help="64-token blocks of the quantize workload (smaller for profiler captures)")
     ap.add_argument("--prefill-sq", type=int, default=4096, help="query tokens of the sparse_prefill workload (smaller for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
