@@ -2,8 +2,11 @@
 //
 // One kernel template serves the three KV sources of the library:
 //   DENSE          paged bf16 cache walked through the block table          (dense decode)
-//   SPARSE_FP8     top-k gather of 656-byte FP8 token records, de-quantised (sparse decode)
+//   SPARSE_FP8     top-k gather of FP8 token records, de-quantised            (sparse decode)
 //   SPARSE_BF16    top-k gather of bf16 rows from a flat [s_kv, d] tensor   (sparse prefill)
+// The two sparse modes exist for both query/key widths of the reference: 576 (656-byte records with four fp32 scales)
+// and 512 (the "MODEL1" form: 448 e4m3 + 64 bf16 RoPE per token, seven e8m0 scales per token stored behind the block's
+// tokens; the RoPE part belongs to V as well).
 // It accepts every head count, h_kv, s_q, page size and index pattern the host API admits and is
 // the kernel used for shapes the tcgen05 kernels do not cover.  It is a correct, reasonably tiled
 // flash-decoding kernel, not the speed-of-light path.
@@ -26,13 +29,13 @@ namespace portable {
 constexpr int BM = 64;            // query rows per CTA
 constexpr int BN = 32;            // tokens per sub-tile
 constexpr int BLK = 64;           // tokens per scheduling block (two sub-tiles)
-constexpr int D_QK = 576;
 constexpr int D_V = 512;
-constexpr int LDK = 584;          // padded row length (elements) of Q / K tiles: 1168 B = 4 words mod 32 banks
+constexpr int LDK = 584;          // padded row length (elements) of Q / K tiles (either width): 1168 B = 4 words mod 32 banks
 constexpr int LDP = 40;           // padded row length of the P tile
 constexpr int LDS = 36;           // padded row length (floats) of the S tile
 constexpr int NTHREADS = 256;
 constexpr int FP8_ROW_BYTES = 656;
+constexpr int M1_ROW_BYTES = 576;      // d_qk 512: 448 e4m3 + 64 bf16 per token; 8 scale bytes per token follow the block's tokens
 
 enum Mode { DENSE = 0, SPARSE_FP8 = 1, SPARSE_BF16 = 2 };
 
@@ -122,7 +125,12 @@ struct Stream {
 };
 
 // Loads sub-tile `st` (tokens [st*32, st*32+32) of the stream) into buffer `buf`.
-template <int MODE>
+// e8m0 scale byte -> fp32: 2^(e - 127); 0 is the subnormal 2^-127, 255 is NaN (as the format defines it)
+__device__ __forceinline__ float e8m0_to_float(uint32_t e) {
+    return __uint_as_float(e == 0 ? 0x00400000u : e == 255 ? 0x7fc00000u : e << 23);
+}
+
+template <int MODE, int DQK>
 __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const Stream& s, int st, int buf) {
     const int tid = threadIdx.x;
     __nv_bfloat16* dst = sm.k[buf];
@@ -131,8 +139,9 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
         const int page = blk < p.max_blocks ? p.block_table[(int64_t)s.req * p.bt_sb + blk] : -1;
         const bool page_ok = page >= 0 && page < p.nblocks[0];
         const __nv_bfloat16* base = p.kc + (int64_t)page * p.k_sblock + (int64_t)s.hk * p.k_shead;
-        for (int c = tid; c < BN * 72; c += NTHREADS) {
-            const int tok = c / 72, ch = c - tok * 72;
+        constexpr int NCH = DQK / 8;
+        for (int c = tid; c < BN * NCH; c += NTHREADS) {
+            const int tok = c / NCH, ch = c - tok * NCH;
             const int pos = st * BN + tok;
             const bool ok = page_ok && pos < s.seqlen;
             if (ch == 0) sm.valid[buf][tok] = ok;
@@ -141,8 +150,9 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
             else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);      // unused cache may hold NaN
         }
     } else if (MODE == SPARSE_BF16) {
-        for (int c = tid; c < BN * 72; c += NTHREADS) {
-            const int tok = c / 72, ch = c - tok * 72;
+        constexpr int NCH = DQK / 8;
+        for (int c = tid; c < BN * NCH; c += NTHREADS) {
+            const int tok = c / NCH, ch = c - tok * NCH;
             const int pos = st * BN + tok;
             int id = -1;
             if (pos < s.len[0]) id = s.idxp[0][pos];
@@ -153,7 +163,9 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
             else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
     } else {
-        // FP8 records: 32 chunks of 16 e4m3 (-> 32 B of bf16) + 8 chunks of 16 B RoPE per token.
+        // FP8 records: NQ chunks of 16 e4m3 (-> 32 B of bf16) + 8 chunks of 16 B RoPE per token.
+        constexpr bool M1 = DQK == 512;
+        constexpr int NQ = M1 ? 28 : 32, NCH = NQ + 8, D_NOPE = NQ * 16;
         const int blk = st >> 1;
         const int scope = blk >= s.nblk0 ? 1 : 0;
         const int pos0 = (scope ? (blk - s.nblk0) : blk) * BLK + (st & 1) * BN;
@@ -161,8 +173,8 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
         const uint8_t* kvb = p.kvb[scope];
         const int pbs = p.pbs[scope];
         const int64_t limit = (int64_t)p.nblocks[scope] * pbs;
-        for (int c = tid; c < BN * 40; c += NTHREADS) {
-            const int tok = c / 40, ch = c - tok * 40;
+        for (int c = tid; c < BN * NCH; c += NTHREADS) {
+            const int tok = c / NCH, ch = c - tok * NCH;
             const int pos = pos0 + tok;
             int id = -1;
             if (pos < s.len[scope]) id = idxp[pos];
@@ -170,31 +182,35 @@ __device__ __forceinline__ void load_subtile(const Params& p, Smem& sm, const St
             if (ch == 0) sm.valid[buf][tok] = ok;
             __nv_bfloat16* drow = dst + tok * LDK;
             if (!ok) {
-                if (ch < 32) {
+                if (ch < NQ) {
                     *reinterpret_cast<uint4*>(drow + ch * 16) = make_uint4(0, 0, 0, 0);
                     *reinterpret_cast<uint4*>(drow + ch * 16 + 8) = make_uint4(0, 0, 0, 0);
                 } else {
-                    *reinterpret_cast<uint4*>(drow + 512 + (ch - 32) * 8) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(drow + D_NOPE + (ch - NQ) * 8) = make_uint4(0, 0, 0, 0);
                 }
                 continue;
             }
-            const uint8_t* rec = kvb + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * FP8_ROW_BYTES;
-            if (ch < 32) {
+            const uint8_t* blk_base = kvb + (int64_t)(id / pbs) * p.kvb_sblock[scope];
+            const int off = id % pbs;
+            const uint8_t* rec = blk_base + (int64_t)off * (M1 ? M1_ROW_BYTES : FP8_ROW_BYTES);
+            if (ch < NQ) {
                 const uint4 raw = __ldg(reinterpret_cast<const uint4*>(rec + ch * 16));
-                const float scale = __ldg(reinterpret_cast<const float*>(rec + 512) + (ch >> 3));
+                // 576: one fp32 scale per 128 values inside the record; 512: one e8m0 scale per 64 values behind the block's tokens
+                const float scale = M1 ? e8m0_to_float(__ldg(blk_base + (int64_t)pbs * M1_ROW_BYTES + off * 8 + (ch >> 2)))
+                                       : __ldg(reinterpret_cast<const float*>(rec + 512) + (ch >> 3));
                 uint4 lo, hi;
                 dequant16(raw, scale, lo, hi);
                 *reinterpret_cast<uint4*>(drow + ch * 16) = lo;
                 *reinterpret_cast<uint4*>(drow + ch * 16 + 8) = hi;
             } else {
-                *reinterpret_cast<uint4*>(drow + 512 + (ch - 32) * 8) =
-                    __ldg(reinterpret_cast<const uint4*>(rec + 528 + (ch - 32) * 16));
+                *reinterpret_cast<uint4*>(drow + D_NOPE + (ch - NQ) * 8) =
+                    __ldg(reinterpret_cast<const uint4*>(rec + (M1 ? D_NOPE : 528) + (ch - NQ) * 16));
             }
         }
     }
 }
 
-template <int MODE>
+template <int MODE, int DQK>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attn_portable_kernel(const Params p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -250,8 +266,9 @@ attn_portable_kernel(const Params p) {
         }
 
         // ---- Q tile -> shared memory (rows beyond the valid ones are zero) -----------------------
-        for (int c = tid; c < BM * 72; c += NTHREADS) {
-            const int r = c / 72, ch = c - r * 72;
+        constexpr int QCH = DQK / 8;
+        for (int c = tid; c < BM * QCH; c += NTHREADS) {
+            const int r = c / QCH, ch = c - r * QCH;
             const int row = row_blk * BM + r;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (row < p.rows) {
@@ -276,12 +293,12 @@ attn_portable_kernel(const Params p) {
                 for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
 
         const int st_begin = blk_begin * 2, st_end = blk_end * 2;
-        if (st_begin < st_end) { load_subtile<MODE>(p, sm, s, st_begin, 0); }
+        if (st_begin < st_end) { load_subtile<MODE, DQK>(p, sm, s, st_begin, 0); }
         cp_async_commit();
 
         for (int st = st_begin; st < st_end; ++st) {
             const int buf = (st - st_begin) & 1;
-            if (st + 1 < st_end) load_subtile<MODE>(p, sm, s, st + 1, buf ^ 1);
+            if (st + 1 < st_end) load_subtile<MODE, DQK>(p, sm, s, st + 1, buf ^ 1);
             cp_async_commit();
             cp_async_wait<1>();
             __syncthreads();
@@ -293,7 +310,7 @@ attn_portable_kernel(const Params p) {
                 const int mid = lane >> 3;
                 const uint32_t b_base = smem_u32(sm.k[buf] + (nh * 16 + (mid >> 1) * 8 + (lane & 7)) * LDK + (mid & 1) * 8);
 #pragma unroll 4
-                for (int kk = 0; kk < D_QK / 16; ++kk) {
+                for (int kk = 0; kk < DQK / 16; ++kk) {
                     uint32_t a[4], bfrag[4];
                     ldmatrix_x4(a, a_base + kk * 32);
                     ldmatrix_x4(bfrag, b_base + kk * 32);
@@ -446,18 +463,18 @@ attn_portable_kernel(const Params p) {
     }
 }
 
-template <int MODE>
+template <int MODE, int DQK = 576>
 static int launch(const Params& p, dim3 grid, cudaStream_t stream) {
     static bool configured[8] = {};
     int dev = 0;
     MLA_CHECK_CUDA(cudaGetDevice(&dev));
     if (dev < 8 && !configured[dev]) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_portable_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_portable_kernel<MODE, DQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
         configured[dev] = true;
     } else if (dev >= 8) {
-        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_portable_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
+        MLA_CHECK_CUDA(cudaFuncSetAttribute(attn_portable_kernel<MODE, DQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Smem)));
     }
-    attn_portable_kernel<MODE><<<grid, NTHREADS, sizeof(Smem), stream>>>(p);
+    attn_portable_kernel<MODE, DQK><<<grid, NTHREADS, sizeof(Smem), stream>>>(p);
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -498,6 +515,7 @@ int launch_sparse_decode_portable(const mla_sparse_decode_args_t& a) {
     p.topk[1] = a.extra_kv ? a.extra_topk : 0; p.topk_len[1] = a.extra_topk_length;
     p.meta = a.meta; p.num_splits = a.num_splits; p.lse_accum = a.lse_accum; p.o_accum = a.o_accum;
     dim3 grid((a.h_q + portable::BM - 1) / portable::BM, a.s_q, a.num_sm_parts);
+    if (a.d_qk == 512) return portable::launch<portable::SPARSE_FP8, 512>(p, grid, (cudaStream_t)a.stream);
     return portable::launch<portable::SPARSE_FP8>(p, grid, (cudaStream_t)a.stream);
 }
 
@@ -513,6 +531,7 @@ int launch_sparse_prefill_portable(const mla_sparse_prefill_args_t& a) {
     p.kvf = (const __nv_bfloat16*)a.kv; p.kvf_ss = a.kv_stride_s; p.s_kv = a.s_kv;
     p.idx[0] = a.indices; p.idx_ss[0] = a.indices_stride_s; p.topk[0] = a.topk; p.topk_len[0] = a.topk_length;
     dim3 grid(a.s_q, (a.h_q + portable::BM - 1) / portable::BM, 1);   // query tokens on x: no 65535 limit
+    if (a.d_qk == 512) return portable::launch<portable::SPARSE_BF16, 512>(p, grid, (cudaStream_t)a.stream);
     return portable::launch<portable::SPARSE_BF16>(p, grid, (cudaStream_t)a.stream);
 }
 

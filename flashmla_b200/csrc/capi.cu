@@ -39,12 +39,14 @@ int current_device_num_sms() {
     return device_num_sms(dev);
 }
 
-static int check_decode_common(const char* who, int b, int s_q, int h_q, int d_qk, int d_v, const void* q,
+// allow_512: the sparse FP8 path also takes the 512-wide ("MODEL1") query / record form
+static int check_decode_common(const char* who, bool allow_512, int b, int s_q, int h_q, int d_qk, int d_v, const void* q,
                                int64_t q_sb, int64_t q_ss, int64_t q_sh, const void* out, int64_t o_sb,
                                int64_t o_ss, int64_t o_sh, const void* lse, const void* meta,
                                const void* num_splits, int num_sm_parts, const void* lse_accum, const void* o_accum) {
     MLA_CHECK_ARG(b > 0 && s_q > 0 && h_q > 0, "%s: b, s_q and h_q must be positive (got %d, %d, %d)", who, b, s_q, h_q);
-    MLA_CHECK_ARG(d_qk == 576, "%s: only head_dim 576 is supported (got %d)", who, d_qk);
+    MLA_CHECK_ARG(d_qk == 576 || (allow_512 && d_qk == 512), "%s: only head_dim %s supported (got %d)", who,
+                  allow_512 ? "576 or 512 is" : "576 is", d_qk);
     MLA_CHECK_ARG(d_v == 512, "%s: only head_dim_v 512 is supported (got %d)", who, d_v);
     MLA_CHECK_ARG(q && out && lse, "%s: q, out and lse must not be null", who);
     MLA_CHECK_ARG(meta && num_splits && num_sm_parts > 0, "%s: tile-scheduler metadata is required", who);
@@ -121,7 +123,7 @@ int mla_combine(const mla_combine_args_t* a) {
 
 int mla_dense_decode_fwd(const mla_dense_decode_args_t* a) {
     MLA_CHECK_ARG(a != nullptr, "mla_dense_decode_fwd: null argument struct");
-    int rc = check_decode_common("mla_dense_decode_fwd", a->b, a->s_q, a->h_q, a->d_qk, a->d_v, a->q, a->q_stride_b,
+    int rc = check_decode_common("mla_dense_decode_fwd", false, a->b, a->s_q, a->h_q, a->d_qk, a->d_v, a->q, a->q_stride_b,
                                  a->q_stride_s, a->q_stride_h, a->out, a->o_stride_b, a->o_stride_s, a->o_stride_h,
                                  a->lse, a->meta, a->num_splits, a->num_sm_parts, a->lse_accum, a->o_accum);
     if (rc) return rc;
@@ -146,7 +148,7 @@ int mla_dense_decode_fwd(const mla_dense_decode_args_t* a) {
 
 int mla_sparse_decode_fwd(const mla_sparse_decode_args_t* a) {
     MLA_CHECK_ARG(a != nullptr, "mla_sparse_decode_fwd: null argument struct");
-    int rc = check_decode_common("mla_sparse_decode_fwd", a->b, a->s_q, a->h_q, a->d_qk, a->d_v, a->q, a->q_stride_b,
+    int rc = check_decode_common("mla_sparse_decode_fwd", true, a->b, a->s_q, a->h_q, a->d_qk, a->d_v, a->q, a->q_stride_b,
                                  a->q_stride_s, a->q_stride_h, a->out, a->o_stride_b, a->o_stride_s, a->o_stride_h,
                                  a->lse, a->meta, a->num_splits, a->num_sm_parts, a->lse_accum, a->o_accum);
     if (rc) return rc;
@@ -154,13 +156,17 @@ int mla_sparse_decode_fwd(const mla_sparse_decode_args_t* a) {
     MLA_CHECK_ARG(a->page_block_size > 0 && a->num_blocks > 0, "mla_sparse_decode_fwd: bad page_block_size / num_blocks");
     MLA_CHECK_ARG(is_aligned16(a->kv) && a->kv_stride_block_bytes % 16 == 0,
                   "mla_sparse_decode_fwd: kv must be 16-byte aligned and its block stride a multiple of 16 bytes");
-    MLA_CHECK_ARG(a->kv_stride_block_bytes >= (int64_t)a->page_block_size * 656,
-                  "mla_sparse_decode_fwd: a kv block must hold page_block_size records of 656 bytes");
+    // 576: 656-byte records; 512: 576 value bytes per token, then 8 scale bytes per token behind the block's tokens
+    const int64_t rec_bytes = a->d_qk == 512 ? 584 : 656;
+    MLA_CHECK_ARG(a->kv_stride_block_bytes >= (int64_t)a->page_block_size * rec_bytes,
+                  "mla_sparse_decode_fwd: a kv block must hold page_block_size records of %d bytes", (int)rec_bytes);
     if (a->extra_kv) {
         MLA_CHECK_ARG(a->extra_indices && a->extra_topk > 0, "mla_sparse_decode_fwd: extra_indices must be provided with extra_kv");
         MLA_CHECK_ARG(a->extra_page_block_size > 0 && a->extra_num_blocks > 0, "mla_sparse_decode_fwd: bad extra page_block_size / num_blocks");
         MLA_CHECK_ARG(is_aligned16(a->extra_kv) && a->extra_kv_stride_block_bytes % 16 == 0,
                       "mla_sparse_decode_fwd: extra_kv must be 16-byte aligned and its block stride a multiple of 16 bytes");
+        MLA_CHECK_ARG(a->extra_kv_stride_block_bytes >= (int64_t)a->extra_page_block_size * rec_bytes,
+                      "mla_sparse_decode_fwd: an extra kv block must hold extra_page_block_size records of %d bytes", (int)rec_bytes);
     } else {
         MLA_CHECK_ARG(!a->extra_indices && !a->extra_topk_length, "mla_sparse_decode_fwd: extra_indices / extra_topk_length need extra_kv");
     }
@@ -179,7 +185,7 @@ int mla_sparse_prefill_fwd(const mla_sparse_prefill_args_t* a) {
     MLA_CHECK_ARG(a != nullptr, "mla_sparse_prefill_fwd: null argument struct");
     MLA_CHECK_ARG(a->s_q > 0 && a->s_kv > 0 && a->h_q > 0 && a->topk > 0, "mla_sparse_prefill_fwd: s_q, s_kv, h_q, topk must be positive");
     MLA_CHECK_ARG(a->h_kv == 1, "mla_sparse_prefill_fwd: h_kv must be 1 (got %d)", a->h_kv);
-    MLA_CHECK_ARG(a->d_qk == 576 && a->d_v == 512, "mla_sparse_prefill_fwd: only d_qk 576 / d_v 512 is supported");
+    MLA_CHECK_ARG((a->d_qk == 576 || a->d_qk == 512) && a->d_v == 512, "mla_sparse_prefill_fwd: only d_qk 576 or 512 with d_v 512 is supported");
     MLA_CHECK_ARG(a->q && a->kv && a->indices && a->out && a->max_logits && a->lse, "mla_sparse_prefill_fwd: null pointer");
     MLA_CHECK_ARG(is_aligned16(a->q) && a->q_stride_s % 8 == 0 && a->q_stride_h % 8 == 0,
                   "mla_sparse_prefill_fwd: q must be 16-byte aligned with strides that are multiples of 8 elements");

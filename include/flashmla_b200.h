@@ -132,20 +132,26 @@ typedef struct {
 } mla_dense_decode_args_t;
 int mla_dense_decode_fwd(const mla_dense_decode_args_t* args);
 
-/* Sparse FP8 MLA decode (656-byte token records, top-k gather).  Replaces
+/* Sparse FP8 MLA decode (top-k gather of FP8 token records).  Two record forms, chosen by d_qk as the reference does
+ * (csrc/api/sparse_decode.h:290-296,318-323):
+ *   d_qk 576: 656 bytes per token = 512 e4m3 | 4 fp32 scales (one per 128 values) | 64 bf16 RoPE; V = the first 512 dims.
+ *   d_qk 512 ("MODEL1"): a block holds page_block_size x [448 e4m3 | 64 bf16 RoPE] (576 bytes per token) followed by
+ *            page_block_size x [7 e8m0 scales (one per 64 values) | 1 pad byte]; the tensor is the
+ *            [num_blocks, page_block_size, 1, 584] view of it and V = all 512 dims.  Served by the all-shape kernel.
+ * Replaces
  * DecodeImplBase::run as driven by sparse_attn_decode_interface
  * (csrc/api/sparse_decode.h:183-495); arguments mirror SparseAttnDecodeParams
  * (csrc/params.h:63-103).  The caller runs mla_combine (with attn_sink) after it. */
 typedef struct {
     int32_t b, s_q, h_q;
-    int32_t d_qk, d_v;                /* 576, 512                                              */
+    int32_t d_qk, d_v;                /* 576 or 512, 512                                       */
     float sm_scale;
 
     const void* q;                    /* bf16 [b, s_q, h_q, d_qk]                              */
     int64_t q_stride_b, q_stride_s, q_stride_h;
 
-    const void* kv;                   /* bytes [num_blocks, page_block_size, 1, 656]           */
-    int64_t kv_stride_block_bytes;    /* kv_stride_row is fixed at 656 bytes                   */
+    const void* kv;                   /* bytes [num_blocks, page_block_size, 1, 656 or 584]    */
+    int64_t kv_stride_block_bytes;    /* the layout inside a block is fixed (see above)        */
     int32_t num_blocks, page_block_size;
     const int32_t* indices;           /* [b, s_q, topk], page*page_block_size + offset, -1 = invalid */
     int64_t indices_stride_b, indices_stride_s;
@@ -213,7 +219,7 @@ size_t mla_workspace_bytes(int b, int s_q, int h_q, int d_v, int num_sm_parts, s
  * SparseAttnFwdParams (csrc/params.h:145-168). */
 typedef struct {
     int32_t s_q, s_kv, h_q, h_kv;     /* h_kv must be 1                                        */
-    int32_t d_qk, d_v, topk;
+    int32_t d_qk, d_v, topk;          /* d_qk 576 or 512 (the latter on the all-shape kernel), d_v 512 */
     float sm_scale;
     const void* q;                    /* bf16 [s_q, h_q, d_qk]                                 */
     int64_t q_stride_s, q_stride_h;

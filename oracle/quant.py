@@ -1,4 +1,4 @@
-"""FP8 KV-cache record (656 bytes per token) : CPU restatement of the
+"""FP8 KV-cache records (656 bytes per token, and the 584-byte "MODEL1" form) : CPU restatement of the
 reference's quantiser / de-quantiser.
 
 TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).
@@ -55,6 +55,61 @@ def dequantize_v32(quant: torch.Tensor) -> torch.Tensor:
     for g in range(NUM_GROUPS):
         out[..., g * GROUP:(g + 1) * GROUP] = nope[..., g * GROUP:(g + 1) * GROUP].float() * scales[..., g].unsqueeze(-1)
     return out.view(nb, bs, 1, D_QK)
+
+
+# ---- "MODEL1" records (d_qk = 512): tests/quant.py:55-75 (quantiser), :106-117 (de-quantiser) -------------------------
+# A block of block_size tokens is stored as
+#   block_size x [448 x float8_e4m3fn "NoPE" | 64 x bfloat16 "RoPE"]      (576 bytes per token)
+#   block_size x [7 x float8_e8m0fnu scales (one per 64 NoPE values) | 1 pad byte]
+# padded up to a multiple of 576 bytes; the tensor handed to the kernels is the [num_blocks, block_size, 1, 584] view of it.
+M1_D, M1_NOPE, M1_ROPE, M1_GROUP, M1_NUM_GROUPS = 512, 448, 64, 64, 7
+M1_BYTES_PER_TOKEN = M1_NOPE + 2 * M1_ROPE + M1_NUM_GROUPS + 1      # 584
+
+
+def model1_block_bytes(block_size: int) -> int:
+    """Bytes from one block to the next (tests/quant.py:57)."""
+    return (block_size * M1_BYTES_PER_TOKEN + 575) // 576 * 576
+
+
+def quantize_model1(blocked_k: torch.Tensor) -> torch.Tensor:
+    """Restates quantize_k_cache, MODEL1 branch (tests/quant.py:55-75): scale = 2^ceil(log2(max(amax/448, 1e-4))) stored as
+    e8m0; value = e4m3(x / scale).  blocked_k [num_blocks, block_size, 1, 512] bf16 -> [num_blocks, block_size, 1, 584]
+    float8_e4m3fn view (block stride model1_block_bytes(block_size))."""
+    nb, bs, h_k, d = blocked_k.shape
+    assert h_k == 1 and d == M1_D
+    x = blocked_k.squeeze(2)
+    res = torch.zeros((nb, model1_block_bytes(bs)), dtype=torch.uint8).view(torch.float8_e4m3fn)[:, :bs * M1_BYTES_PER_TOKEN]   # pad bytes 0
+    data = res[:, :bs * 576].view(nb, bs, 576)
+    nope = data[:, :, :M1_NOPE]
+    rope = data[:, :, M1_NOPE:].view(blocked_k.dtype)
+    scales = res[:, bs * 576:].view(nb, bs, 8)[:, :, :M1_NUM_GROUPS].view(torch.float8_e8m0fnu)
+    rope[:] = x[..., M1_NOPE:]
+    for g in range(M1_NUM_GROUPS):
+        grp = x[..., g * M1_GROUP:(g + 1) * M1_GROUP]
+        s = grp.abs().max(dim=-1).values.float() / 448.0
+        s = torch.pow(2, torch.clamp_min(s, 1e-4).log2().ceil())
+        scales[:, :, g] = s.to(torch.float8_e8m0fnu)
+        nope[:, :, g * M1_GROUP:(g + 1) * M1_GROUP] = (grp.float() / s.unsqueeze(-1).float()).to(torch.float8_e4m3fn)
+    return res.view(nb, bs, 1, M1_BYTES_PER_TOKEN)
+
+
+def dequantize_model1(quant: torch.Tensor) -> torch.Tensor:
+    """Restates dequantize_k_cache, MODEL1 branch (tests/quant.py:106-117): bf16(e4m3) * bf16(e8m0 scale) in bf16, RoPE
+    copied.  Returns [num_blocks, block_size, 1, 512] bf16."""
+    nb, bs, h_k, nbytes = quant.shape
+    assert h_k == 1 and nbytes == M1_BYTES_PER_TOKEN
+    qv = quant if quant.dtype == torch.float8_e4m3fn else quant.view(torch.float8_e4m3fn)
+    flat = qv.reshape(nb, -1) if qv.is_contiguous() else qv.view(nb, -1)
+    data = flat[:, :bs * 576].view(nb, bs, 576)
+    nope = data[:, :, :M1_NOPE]
+    rope = data[:, :, M1_NOPE:].view(torch.bfloat16)
+    scales = flat[:, bs * 576:].view(nb, bs, 8)[:, :, :M1_NUM_GROUPS].view(torch.float8_e8m0fnu)
+    out = torch.empty((nb, bs, M1_D), dtype=torch.bfloat16)
+    out[..., M1_NOPE:] = rope
+    for g in range(M1_NUM_GROUPS):
+        out[..., g * M1_GROUP:(g + 1) * M1_GROUP] = nope[..., g * M1_GROUP:(g + 1) * M1_GROUP].to(torch.bfloat16) * \
+            scales[:, :, g].to(torch.bfloat16).unsqueeze(-1)
+    return out.view(nb, bs, 1, M1_D)
 
 
 def abs_to_physical_indices(abs_indices: torch.Tensor, block_table: torch.Tensor, block_size: int) -> torch.Tensor:

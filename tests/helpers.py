@@ -111,3 +111,13 @@ def check_schedule_properties(meta, num_splits, eff_seqlens, num_sm_parts, block
         last_is_split = int(len(pieces[end_req]) > 1)
         assert first_split == first_is_split, f"partition {p}: is_first_req_splitted {first_split}, request has {len(pieces[begin_req])} pieces"
         assert last_split == last_is_split, f"partition {p}: is_last_req_splitted {last_split}, request has {len(pieces[end_req])} pieces"
+
+
+def model1_cache_from_bytes(kv_bytes: torch.Tensor, block_stride: int, device="cpu") -> torch.Tensor:
+    """Rebuilds a d_qk = 512 FP8 cache from its [num_blocks, block_size, 1, 584] bytes: the blocks are laid out again
+    `block_stride` bytes apart (a block is block_size x 576 value bytes followed by block_size x 8 scale bytes, padded to a
+    multiple of 576), and the [num_blocks, block_size, 1, 584] float8_e4m3fn view of that buffer is returned."""
+    nb, bs = kv_bytes.shape[:2]
+    buf = torch.zeros(nb, block_stride, dtype=torch.uint8, device=device)
+    buf[:, :bs * 584] = kv_bytes.reshape(nb, bs * 584).to(device)
+    return buf.view(torch.float8_e4m3fn)[:, :bs * 584].view(nb, bs, 1, 584)

@@ -62,6 +62,8 @@ def test_config1_tiny():
     # two row blocks: Q boxes of 2 tokens x 64 heads per block / a group size that does not divide a row block
     # (Q is then loaded by the kernel's own threads)
     (4, 64, 1, True), (4, 48, 1, True),
+    # eight KV heads: 8 and 16 query heads per KV head
+    (1, 64, 8, False), (2, 128, 8, True),
 ])
 def test_shape_grid(s_q, h_q, h_kv, causal):
     seqlens = [140, 4096 // 8 + 3, 20, 0, 64, 1, 1000, 65]
@@ -69,7 +71,8 @@ def test_shape_grid(s_q, h_q, h_kv, causal):
 
 
 @pytest.mark.parametrize("impl", [1, 2])
-@pytest.mark.parametrize("s_q,h_q,h_kv,causal", [(1, 128, 1, False), (2, 128, 1, True), (2, 48, 2, True), (1, 16, 1, False)])
+@pytest.mark.parametrize("s_q,h_q,h_kv,causal", [(1, 128, 1, False), (2, 128, 1, True), (2, 48, 2, True), (1, 16, 1, False),
+                                                 (1, 128, 8, True)])
 def test_both_kernel_families(impl, s_q, h_q, h_kv, causal):
     """The portable kernel (1) and the tcgen05 kernel (2) must both match the oracle on the same inputs."""
     seqlens = [140, 515, 20, 0, 64, 1, 1000, 65, 4096]

@@ -59,6 +59,37 @@ def test_sparse_prefill_oracle_matches_reference(golden_dir):
         assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
 
 
+def test_model1_oracle_matches_reference(golden_dir):
+    """d_qk = 512: 584-byte records with e8m0 scales (decode) and 512-wide rows (prefill)."""
+    from tests.helpers import model1_cache_from_bytes
+    m = _load(golden_dir, "model1.pt")
+    c = m["quant"]
+    qz = quant.quantize_model1(c["x"])
+    assert qz.stride(0) == c["quant_stride0"] == quant.model1_block_bytes(64)
+    nb, bs = c["x"].shape[:2]
+    mine, ref = qz.contiguous().view(torch.uint8).view(nb, -1), c["quant_bytes"].view(nb, -1)
+    assert torch.equal(mine[:, :bs * 576], ref[:, :bs * 576])                              # values and RoPE
+    assert torch.equal(mine[:, bs * 576:].view(nb, bs, 8)[..., :7], ref[:, bs * 576:].view(nb, bs, 8)[..., :7])   # scales (byte 8 is padding)
+    dq = quant.dequantize_model1(model1_cache_from_bytes(c["quant_bytes"], c["quant_stride0"]))
+    assert torch.equal(dq.view(torch.int16), c["dequant"].view(torch.int16))
+    for c in m["decode"]:
+        kv = quant.dequantize_model1(model1_cache_from_bytes(c["kv_bytes"], c["kv_stride0"]))
+        extra = None
+        if "extra_kv_bytes" in c:
+            extra = quant.dequantize_model1(model1_cache_from_bytes(c["extra_kv_bytes"], c["extra_kv_stride0"]))
+        out, lse = attention.sparse_decode(
+            c["q"], kv, c["indices"], c["sm_scale"], c["d_v"], c["attn_sink"], c["topk_length"],
+            extra, c.get("extra_indices"), c.get("extra_topk_length"))
+        assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
+        assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
+    for c in m["prefill"]:
+        out, mx, lse = attention.sparse_prefill(c["q"], c["kv"], c["indices"], c["sm_scale"], c["d_v"],
+                                                c["attn_sink"], c["topk_length"], row_chunk=4)
+        assert check_close("out", out, c["out"], abs_tol=1e-6, rel_tol=BF16_ULP, cos_diff_tol=1e-8)
+        assert check_close("max_logits", mx, c["max_logits"], abs_tol=2e-6, rel_tol=1e-6)
+        assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
+
+
 def test_uniform_costs_one_partition_per_request_never_split():
     """With equal request costs and as many partitions as requests the greedy scheduler cuts at every request boundary
     (the sparse decode path relies on this to skip the combine kernel)."""
