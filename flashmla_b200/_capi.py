@@ -94,7 +94,7 @@ class QuantizeArgs(Structure):
         ("x", c_void_p), ("x_stride_block", c_int64), ("x_stride_row", c_int64),
         ("num_blocks", c_int32), ("block_size", c_int32),
         ("out", c_void_p), ("out_stride_block_bytes", c_int64),
-        ("pow2_scale", c_int32), ("_pad", c_int32), ("stream", c_void_p),
+        ("pow2_scale", c_int32), ("layout", c_int32), ("stream", c_void_p),
     ]
 
 

@@ -257,7 +257,10 @@ int mla_dense_decode_noalloc(const mla_dense_decode_args_t* args);
  * flash_mla/flash_mla_interface.py:92-98): scale = amax/448 per group of 128 values (clamped to 1e-30), or with
  * pow2_scale != 0 the smallest power of two >= max(amax/448, 1e-4); q = e4m3(x / scale).
  * x: [num_blocks, block_size, 576] bf16 (strides in elements); out: [num_blocks, block_size, 656] bytes with a free
- * block stride (>= block_size * 656, multiple of 16). */
+ * block stride (>= block_size * 656, multiple of 16).
+ * layout 1 writes the 512-wide "MODEL1" form instead (tests/quant.py:55-75): x [num_blocks, block_size, 512]; per block
+ * block_size x (448 e4m3 | 64 bf16) followed by block_size x (7 e8m0 scales | 1 zero byte); one power-of-two scale per 64
+ * values (pow2_scale is ignored); block stride >= block_size * 584 (the reference pads it to a multiple of 576). */
 typedef struct {
     const void* x;
     int64_t x_stride_block, x_stride_row;
@@ -265,7 +268,7 @@ typedef struct {
     void* out;
     int64_t out_stride_block_bytes;
     int32_t pow2_scale;
-    int32_t _pad;
+    int32_t layout;                   /* 0: 656-byte records (d 576); 1: MODEL1 (d 512)        */
     void* stream;
 } mla_quantize_args_t;
 int mla_quantize_fp8_kvcache(const mla_quantize_args_t* args);
