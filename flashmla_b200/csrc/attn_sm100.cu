@@ -138,6 +138,7 @@ struct Params {
     int b, s_q, h_q, h_kv, g, rows, causal, num_blocks;
     int head_chunks;                       // dense mode: 64-column chunks between two kv heads of a cache row
     int max_blocks;                        // dense mode: width of the block table
+    int no_chunk8;                         // prefill with 512-wide rows: the ninth 64-column chunk of Q and K is all zeros
     float scale_log2;
     long long wait_limit;                  // SM cycles after which a barrier wait gives up
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
@@ -360,14 +361,14 @@ __device__ __noinline__ void zero_v_rows(uint8_t* vst, int first) {
 // strides do not fit a TMA box (several times slower than the boxes; kept out of line, it is rarely taken).
 // Warpgroup `half` takes its share of the chunks: to tensor memory, in the gather modes chunks 7 / 8 to shared memory.
 template <int MODE>
-__device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qrow, bool row_ok, int half, int r, uint32_t tlane) {
+__device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qrow, bool row_ok, int half, int r, uint32_t tlane, bool no_chunk8) {
     using L = Lay<MODE>;
     const int c_begin = half ? L::Q_SPLIT : 0, c_end = half ? L::Q_TMEM_CHUNKS : L::Q_SPLIT, c_smem = half ? 8 : 7;
 #pragma unroll 1
     for (int c = c_begin; c < c_end + (L::WIDE ? 0 : 1); ++c) {
         const int chunk = c < c_end ? c : c_smem;
         uint32_t v[32];
-        if (row_ok) {
+        if (row_ok && !(no_chunk8 && chunk == 8)) {
             const uint4* src = reinterpret_cast<const uint4*>(qrow + chunk * 64);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -905,8 +906,10 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         for (int q4 = 0; q4 < 8; ++q4) {
                             const int rr = 4 * q4 + (lane >> 3);
                             const int rid = __shfl_sync(0xffffffffu, row_id, rr);
-                            const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + (64 + c) * 8;
-                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, rid < 0 ? 0u : 16u);
+                            // (rows of 512 columns have no ninth chunk: zeros, as for an invalid token)
+                            const bool none = rid < 0 || p.no_chunk8;
+                            const __nv_bfloat16* src = none ? p.kv : p.kv + (int64_t)rid * p.kv_ss + (64 + c) * 8;
+                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, none ? 0u : 16u);
                         }
                     }
                     cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot2]));
@@ -1022,7 +1025,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         tmem_wait_st();
                         if (!wt.aborted) mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
                     } else {
-                        load_q_by_threads<MODE>(sm, qrow, row_ok, half, r, tlane);
+                        load_q_by_threads<MODE>(sm, qrow, row_ok, half, r, tlane, p.no_chunk8 != 0);
                     }
                     tmem_wait_st();
                     fence_proxy_async_smem();
@@ -1441,7 +1444,7 @@ bool dense_decode_sm100_supports(const mla_dense_decode_args_t& a) {
 // tokens.  Returns false (the kernels then load every Q with their own threads) when Q's base or strides do not meet
 // TMA's 16-byte rules or the driver rejects the map.
 static bool encode_q_map(CUtensorMap* qmap, const void* q, int b, int s_q, int h_q, int64_t sb, int64_t ss, int64_t sh,
-                         int box_h, int box_t, int* box_bytes, bool fp16 = false) {
+                         int box_h, int box_t, int* box_bytes, bool fp16 = false, int d_qk = 576) {
     using namespace sm100;
     static const bool enabled = [] { const char* e = getenv("MLA_Q_TMA"); return !(e && e[0] == '0'); }();
     EncodeTiledFn encode = get_encode_fn();
@@ -1452,7 +1455,8 @@ static bool encode_q_map(CUtensorMap* qmap, const void* q, int b, int s_q, int h
     if ((reinterpret_cast<uintptr_t>(q) & 15) || sb <= 0 || ss <= 0 || sh <= 0 || (sb % 8) || (ss % 8) || (sh % 8)) return false;
     if (sb * 2 >= (1ll << 40) || ss * 2 >= (1ll << 40) || sh * 2 >= (1ll << 40)) return false;
     if (box_h < 1 || box_h > 256 || box_t < 1 || box_t > 256 || box_h * box_t > ROWS) return false;
-    cuuint64_t dims[4] = {576, (cuuint64_t)h_q, (cuuint64_t)s_q, (cuuint64_t)b};
+    // (512-wide rows: the ninth box of a request lies wholly outside the tensor and arrives as zeros)
+    cuuint64_t dims[4] = {(cuuint64_t)d_qk, (cuuint64_t)h_q, (cuuint64_t)s_q, (cuuint64_t)b};
     cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)ss * 2, (cuuint64_t)sb * 2};
     cuuint32_t box[4] = {64, (cuuint32_t)box_h, (cuuint32_t)box_t, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
@@ -1544,7 +1548,7 @@ int launch_dense_decode_sm100(const mla_dense_decode_args_t& a) {
 }
 
 bool sparse_prefill_sm100_supports(const mla_sparse_prefill_args_t& a) {
-    if (a.d_qk != 576 || a.d_v != 512 || a.h_kv != 1) return false;
+    if ((a.d_qk != 576 && a.d_qk != 512) || a.d_v != 512 || a.h_kv != 1) return false;
     if (a.kv_stride_s <= 0 || a.kv_stride_s % 8 || a.kv_stride_s >= ((int64_t)1 << 39)) return false;
     if (!(a.sm_scale > 0.f)) return false;
     if (a.h_q > 128 * 65535) return false;
@@ -1566,6 +1570,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     p.attn_sink = a.attn_sink;
     p.indices = a.indices; p.idx_ss = a.indices_stride_s; p.topk = a.topk; p.topk_len = a.topk_length; p.s_kv = a.s_kv;
     p.kv = (const __nv_bfloat16*)a.kv; p.kv_ss = a.kv_stride_s;
+    p.no_chunk8 = a.d_qk == 512 ? 1 : 0;
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
 
@@ -1579,7 +1584,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     CUtensorMap qmap;
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, 1, a.s_q, a.h_q, 0, a.q_stride_s, a.q_stride_h, a.h_q < ROWS ? a.h_q : ROWS, 1,
-                           &p.q_box_bytes) ? 1 : 0;
+                           &p.q_box_bytes, false, a.d_qk) ? 1 : 0;
     MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_PREFILL, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, kmap, kmap, qmap, p));
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;

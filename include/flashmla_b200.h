@@ -219,7 +219,7 @@ size_t mla_workspace_bytes(int b, int s_q, int h_q, int d_v, int num_sm_parts, s
  * SparseAttnFwdParams (csrc/params.h:145-168). */
 typedef struct {
     int32_t s_q, s_kv, h_q, h_kv;     /* h_kv must be 1                                        */
-    int32_t d_qk, d_v, topk;          /* d_qk 576 or 512 (the latter on the all-shape kernel), d_v 512 */
+    int32_t d_qk, d_v, topk;          /* d_qk 576 or 512, d_v 512                              */
     float sm_scale;
     const void* q;                    /* bf16 [s_q, h_q, d_qk]                                 */
     int64_t q_stride_s, q_stride_h;
