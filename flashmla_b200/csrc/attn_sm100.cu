@@ -309,6 +309,11 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return pack16<false>(lo, hi); }
 
+// e8m0 scale byte -> fp32: 2^(e - 127); 0 is the subnormal 2^-127, 255 is NaN (as the format defines it)
+__device__ __forceinline__ float e8m0_to_float(uint32_t e) {
+    return __uint_as_float(e == 0 ? 0x00400000u : e == 255 ? 0x7fc00000u : e << 23);
+}
+
 // 16 e4m3 values (one uint4) times an fp32 scale -> 16 bf16 (two uint4), one rounding: bf16(fp32(e4m3) * scale).
 // (A conversion-free variant that places the e4m3 magnitude bits into an fp32 word and multiplies by scale * 2^120 is
 // bit-identical but needs more instructions per value and measured slower.)
@@ -390,8 +395,10 @@ __device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qr
     }
 }
 
-// FP16: q, the cache and out are fp16 instead of bf16 (dense mode only); accumulation is fp32 either way.
-template <int MODE, bool FP16>
+// ALT selects the second data format of a mode.  Dense mode: q, the cache and out are fp16 instead of bf16 (accumulation
+// is fp32 either way).  Sparse FP8 decode: the 512-wide record form (448 e4m3 + 64 bf16 RoPE per token, seven e8m0 scales
+// per token stored behind the block's tokens, V = all 512 dims): chunk 7 of a tile is the RoPE part, chunk 8 is zeros.
+template <int MODE, bool ALT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
 attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                   const __grid_constant__ CUtensorMap qmap, const Params p) {
@@ -399,6 +406,9 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     using L = Lay<MODE>;
     constexpr int NKS = L::NKS;
     constexpr bool DENSE = MODE == MODE_DENSE;
+    constexpr bool FP16 = ALT && MODE == MODE_DENSE;
+    constexpr bool M1 = ALT && MODE == MODE_SPARSE_DECODE;
+    constexpr int REC_BYTES = M1 ? 576 : 656;              // bytes between two tokens' values inside a block
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
     const uint32_t cta_rank = cluster_ctarank();          // 0 = score CTA, 1 = value CTA
@@ -760,17 +770,26 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int scope = blk >= w.nblk0 ? 1 : 0;
                     const int pbs = p.pbs[scope];
                     if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return nullptr;
-                    return p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * 656;
+                    return p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] + (int64_t)(id % pbs) * REC_BYTES;
                 };
-                auto scales_of = [&](const uint8_t* rec) {
-                    return rec ? __ldg(reinterpret_cast<const float4*>(rec + 512)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                // the token's scales as they are stored: four fp32 inside the record, or (512-wide form) eight bytes -
+                // seven e8m0 exponents and a pad - behind the block's tokens, carried in the first two words
+                auto scales_of = [&](int blk, int id, const uint8_t* rec) {
+                    if (!rec) return make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (!M1) return __ldg(reinterpret_cast<const float4*>(rec + 512));
+                    const int scope = blk >= w.nblk0 ? 1 : 0;
+                    const int pbs = p.pbs[scope];
+                    const uint2 e = __ldg(reinterpret_cast<const uint2*>(p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] +
+                                                                         (int64_t)pbs * 576 + (int64_t)(id % pbs) * 8));
+                    return make_float4(__uint_as_float(e.x), __uint_as_float(e.y), 0.f, 0.f);
                 };
                 if (cta_rank == 0) {
                     // warp gw owns tokens 32*gw .. 32*gw+31 of the tile; lane l looks up token 32*gw + l
                     const int tok = gw * 32 + lane;
                     const int myblk = w.blk_begin + (tok >> 6);              // this lane's block of tile 0
-                    const uint8_t* rec_next = rec_of(myblk, load_id(myblk, tok & 63));
-                    float4 sc_next = scales_of(rec_next);
+                    const int id_first = load_id(myblk, tok & 63);
+                    const uint8_t* rec_next = rec_of(myblk, id_first);
+                    float4 sc_next = scales_of(myblk, id_first, rec_next);
                     int id_next = load_id(myblk + 2, tok & 63);              // tile 1
                     for (int i = 0; i < w.ntiles; ++i, ++g) {
                         const uint8_t* rec = rec_next;
@@ -782,7 +801,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         reinterpret_cast<float4*>(sm.data + L::SC_SCALES)[(g & 1) * ROWS + tok] = sc_cur;
                         __threadfence_block();
                         rec_next = rec_of(myblk + 2 * (i + 1), id_next);
-                        sc_next = scales_of(rec_next);
+                        sc_next = scales_of(myblk + 2 * (i + 1), id_next, rec_next);
                         id_next = load_id(myblk + 2 * (i + 2), tok & 63);
                         if (ring_lent) { WAIT_WARP_OR_LEAVE(wt, false, &sm.ring_released, nreq_g & 1, 211); ring_lent = false; }
 #pragma unroll 1
@@ -790,14 +809,17 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             WAIT_WARP_OR_LEAVE(wt, false, &sm.kv_empty[grp], ((ks / NKS) & 1) ^ 1, 201);
                             // copy: groups 0, 1: 12 raw pieces per row; group 2: 8 raw pieces + 8 RoPE pieces per row.  A copy
                             // instruction costs the warp the same whatever its active lanes: each one serves two rows.
-                            const int per_row = grp < 2 ? 12 : 16;
-                            const int sub = grp < 2 ? (lane >= 12) + (lane >= 24) : lane >> 4, ql = lane - sub * per_row;
+                            // (512-wide form: every group has 12 pieces per row; group 2 is chunk 6 - 4 raw pieces - and the 8 RoPE
+                            // pieces, which are chunk 7; chunk 8 is zeroed by the converting threads)
+                            const int per_row = (grp < 2 || M1) ? 12 : 16;
+                            const int sub = (grp < 2 || M1) ? (lane >= 12) + (lane >= 24) : lane >> 4, ql = lane - sub * per_row;
                             const bool active = sub < 2;
-                            const bool is_rope = grp == 2 && ql >= 8;
+                            constexpr int N_RAW2 = M1 ? 4 : 8;               // raw pieces of group 2
+                            const bool is_rope = grp == 2 && ql >= N_RAW2;
                             const int q = grp * 12 + ql;                      // raw piece index in the row
-                            const int srcoff = is_rope ? 528 + (ql - 8) * 16 : q * 16;
-                            const int dslot = is_rope ? ql - 8 : 2 * (q & 3) + 1;
-                            const uint32_t dst0 = kring + (is_rope ? 8 : (q >> 2)) * K_CHUNK_BYTES + gw * 32 * 128;
+                            const int srcoff = is_rope ? (M1 ? 448 : 528) + (ql - N_RAW2) * 16 : q * 16;
+                            const int dslot = is_rope ? ql - N_RAW2 : 2 * (q & 3) + 1;
+                            const uint32_t dst0 = kring + (is_rope ? (M1 ? 7 : 8) : (q >> 2)) * K_CHUNK_BYTES + gw * 32 * 128;
 #pragma unroll 8
                             for (int u = 0; u < 16; ++u) {
                                 const int rr = 2 * u + (active ? sub : 0);
@@ -830,11 +852,24 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                                 const int q = nh * 16 + ql;
                                 const uint32_t dst0 = vring + slot * V_SLOT_BYTES + (ql >> 2) * BOX_BYTES + gw * 16 * 128;
                                 const int dslot = 2 * (ql & 3) + 1;
+                                // (512-wide form, second half: 12 raw pieces - chunks 4, 5, 6 - and, below, the RoPE part as chunk 7)
+                                const bool piece_ok = !M1 || nh == 0 || ql < 12;
 #pragma unroll
                                 for (int u = 0; u < 8; ++u) {
                                     const int rr = 2 * u + sub;
                                     const uint8_t* r = shfl_ptr(rec, rr);
-                                    cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
+                                    if (piece_ok)
+                                        cp_async16_zfill(dst0 + rr * 128 + ((dslot ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + q * 16, r ? 16u : 0u);
+                                }
+                                if (M1 && nh == 1) {
+                                    const int piece = lane & 7;
+                                    const uint32_t dst7 = vring + slot * V_SLOT_BYTES + 3 * BOX_BYTES + gw * 16 * 128;
+#pragma unroll
+                                    for (int u = 0; u < 4; ++u) {
+                                        const int rr = 4 * u + (lane >> 3);
+                                        const uint8_t* r = shfl_ptr(rec, rr);
+                                        cp_async16_zfill(dst7 + rr * 128 + ((piece ^ (rr & 7)) << 4), (r ? r : p.kvb[0]) + 448 + piece * 16, r ? 16u : 0u);
+                                    }
                                 }
                                 cp_async_arrive_noinc(smem_addr(&sm.raw_full[slot]));      // warps 8-11 expand the pieces
                             }
@@ -974,12 +1009,15 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     if (!wt_fast.template wait<false>(&sm.raw_full[grp], tile & 1, 205)) { wt.aborted = true; return; }
                     // the tile's scales were stored (and fenced) by the gather warps before they issued its first copies
                     if (grp == 0) sc = reinterpret_cast<const float4*>(sm.data + L::SC_SCALES)[(tile & 1) * ROWS + r];
-                    const int nconv = grp < 2 ? 3 : 2;                 // group 2: chunks 6, 7 and the RoPE chunk (copied as it is)
+                    // group 2: chunks 6, 7 and the RoPE chunk (copied as it is); 512-wide form: chunk 6, the RoPE chunk and zeros
+                    const int nconv = grp < 2 ? 3 : (M1 ? 1 : 2);
 #pragma unroll 1
                     for (int cj = 0; cj < nconv; ++cj) {
                         const int j = grp * 3 + cj, sg = j >> 1;
                         uint8_t* rowp = sm.data + L::SC_KRING + j * K_CHUNK_BYTES + r * 128;
-                        const float scale = sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w;
+                        // one fp32 scale per two chunks, or one e8m0 exponent byte per chunk (byte j of the first two words)
+                        const float scale = M1 ? e8m0_to_float((__float_as_uint(j < 4 ? sc.x : sc.y) >> (8 * (j & 3))) & 0xffu)
+                                               : (sg == 0 ? sc.x : sg == 1 ? sc.y : sg == 2 ? sc.z : sc.w);
                         uint4 raw[2];
 #pragma unroll
                         for (int k2 = 0; k2 < 2; ++k2) raw[k2] = *reinterpret_cast<const uint4*>(rowp + (((2 * (half + 2 * k2) + 1) ^ sw) << 4));
@@ -991,6 +1029,12 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             *reinterpret_cast<uint4*>(rowp + (((2 * k) ^ sw) << 4)) = lo;
                             *reinterpret_cast<uint4*>(rowp + (((2 * k + 1) ^ sw) << 4)) = hi;
                         }
+                    }
+                    if (M1 && grp == 2) {
+                        // the ninth chunk of a 512-wide row does not exist: zeros (this thread's half of the token's row)
+                        uint8_t* row8 = sm.data + L::SC_KRING + 8 * K_CHUNK_BYTES + r * 128;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(row8 + (((half * 4 + k) ^ sw) << 4)) = make_uint4(0, 0, 0, 0);
                     }
                     fence_proxy_async_smem();          // generic-proxy stores -> visible to the tensor core's reads
                     mbar_arrive(smem_addr(&sm.kv_full[grp]));
@@ -1280,6 +1324,11 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                     const int scope = blk >= w.nblk0 ? 1 : 0;
                     const int pbs = p.pbs[scope];
                     if (id < 0 || (int64_t)id >= (int64_t)p.nblocks[scope] * pbs) return make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (M1) {
+                        const uint2 e = __ldg(reinterpret_cast<const uint2*>(p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] +
+                                                                             (int64_t)pbs * 576 + (int64_t)(id % pbs) * 8));
+                        return make_float4(__uint_as_float(e.x), __uint_as_float(e.y), 0.f, 0.f);
+                    }
                     return __ldg(reinterpret_cast<const float4*>(p.kvb[scope] + (int64_t)(id / pbs) * p.kvb_sblock[scope] +
                                                                  (int64_t)(id % pbs) * 656 + 512));
                 };
@@ -1296,9 +1345,15 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         for (int nh = 0; nh < 2; ++nh, ++ks) {
                             const uint32_t slot = ks % NVS;
                             WAIT_WARP_OR_LEAVE(wt_fast, false, &sm.raw_full[slot], (ks / NVS) & 1, 206);
-                            const float scale = hb ? (nh ? sc.w : sc.y) : (nh ? sc.z : sc.x);
+                            float scale = hb ? (nh ? sc.w : sc.y) : (nh ? sc.z : sc.x);
+                            // (512-wide form: one exponent byte per chunk; chunk 7 is the RoPE part, copied as it is)
+                            const int nconv = (M1 && nh == 1 && hb == 1) ? 1 : 2;
 #pragma unroll 1
-                            for (int cj = 0; cj < 2; ++cj) {
+                            for (int cj = 0; cj < nconv; ++cj) {
+                                if (M1) {
+                                    const int c = nh * 4 + hb * 2 + cj;
+                                    scale = e8m0_to_float((__float_as_uint(c < 4 ? sc.x : sc.y) >> (8 * (c & 3))) & 0xffu);
+                                }
                                 uint8_t* rowp = sm.data + VA_VRING + slot * V_SLOT_BYTES + (hb * 2 + cj) * BOX_BYTES + trow * 128;
                                 uint4 raw[4];
 #pragma unroll
@@ -1591,7 +1646,7 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
 }
 
 bool sparse_decode_sm100_supports(const mla_sparse_decode_args_t& a) {
-    if (a.d_qk != 576 || a.d_v != 512) return false;
+    if ((a.d_qk != 576 && a.d_qk != 512) || a.d_v != 512) return false;
     if (a.h_q > 128 || a.s_q > 65535 || a.num_sm_parts > 65535) return false;
     if (!(a.sm_scale > 0.f)) return false;
     if (reinterpret_cast<uintptr_t>(a.o_accum) & 31) return false;      // split partials leave with 256-bit stores
@@ -1620,15 +1675,21 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     p.sidx[1] = a.extra_indices; p.sidx_sb[1] = a.extra_indices_stride_b; p.sidx_ss[1] = a.extra_indices_stride_s;
     p.stopk[1] = a.extra_kv ? a.extra_topk : 0; p.stopk_len[1] = a.extra_topk_length;
 
-    static bool configured[64] = {};
-    if (int rc = configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, configured)) return rc;
+    const bool m1 = a.d_qk == 512;                  // the 512-wide record form: the ninth chunk of Q and K is zeros
+    p.no_chunk8 = m1 ? 1 : 0;
+    static bool configured[64] = {}, configured_m1[64] = {};
+    if (int rc = m1 ? configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, true>, configured_m1)
+                    : configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, configured)) return rc;
     CUtensorMap unused_map, qmap;
     memset(&unused_map, 0, sizeof(unused_map));     // this mode gathers K and V with its own threads
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, a.b, a.s_q, a.h_q, a.q_stride_b, a.q_stride_s, a.q_stride_h,
-                           a.h_q < ROWS ? a.h_q : ROWS, 1, &p.q_box_bytes) ? 1 : 0;
+                           a.h_q < ROWS ? a.h_q : ROWS, 1, &p.q_box_bytes, false, a.d_qk) ? 1 : 0;
     dim3 grid(2, a.s_q, a.num_sm_parts);
-    MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, unused_map, unused_map, qmap, p));
+    if (m1)
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_SPARSE_DECODE, true>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, unused_map, unused_map, qmap, p));
+    else
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, unused_map, unused_map, qmap, p));
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }

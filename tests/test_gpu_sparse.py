@@ -74,6 +74,28 @@ def test_sparse_decode_cases(b, s_q, h_q, s_kv, topk, pow2, sink):
     assert_lse_close("lse", lse, ref_lse)
 
 
+def test_sparse_decode_lengths_come_and_go_on_one_sched_meta():
+    """The reference accepts calls with and without topk_length on the same sched_meta (its partition count does not depend
+    on them); here the two cases use different partition rules, so the stored schedule is made again when they switch."""
+    import flashmla_b200 as fm
+    from tests import workloads as W
+    b, s_q, h_q, s_kv, topk = 6, 1, 64, 1024, 512
+    d = W.sparse_decode_inputs(b, s_q, h_q, s_kv, topk, seed=3, device="cpu")
+    kv_deq = quant.dequantize_v32(d["kv_fp8"])
+    tl = torch.tensor([512, 0, 100, 511, 64, 300], dtype=torch.int32)
+    meta, _ = fm.get_mla_metadata()
+    q, kv, idx = d["q"].to(DEV), d["kv_fp8"].to(DEV), d["indices"].to(DEV)
+    for lengths in (None, tl, None, tl):
+        out, lse = fm.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, 576 ** -0.5, False, True, idx, None, None, None,
+                                             _dev(lengths), None)
+        torch.cuda.synchronize()
+        fm.check_status()
+        ref_out, ref_lse = attention.sparse_decode(d["q"], kv_deq, d["indices"], 576 ** -0.5, 512, None, lengths)
+        assert_out_close("out", out, ref_out)
+        assert_lse_close("lse", lse, ref_lse)
+        assert meta.uniform_costs == (lengths is None)
+
+
 def test_sparse_decode_all_invalid_and_unused_nan():
     """A request whose indices are all -1 gives out = 0 and lse = +inf; cache rows that no index refers to may
     hold NaN bytes without leaking into the result."""
