@@ -93,15 +93,19 @@ def make_workload(name, device, seed, prefill_sq=4096):
                     bytes=S * D_QK * 2 + per * h_q * D_QK * 2 + per * h_q * D_V * 2,
                     flops=2.0 * h_q * S * (D_QK + D_V),
                     desc=f"dense bf16 MLA decode b={b_total} total (batch-sharded) h_q=128 s_q=1 seqlens lognormal(median 8192, sigma 1) clip[256,131072]")
-    if name == "sparse_decode":
+    if name in ("sparse_decode", "sparse_decode_m1"):
+        # (_m1: the 512-wide "MODEL1" form - 584-byte records with e8m0 scales, d_qk = 512 - a side measurement)
+        m1 = name == "sparse_decode_m1"
+        d_qk, rec = (512, 584) if m1 else (D_QK, 656)
         b, h_q, s_kv, topk = 64, 128, 32768, 2048
-        d = W.sparse_decode_inputs(b, 1, h_q, s_kv, topk, seed=seed, device=device, data_on_device=True)
+        d = W.sparse_decode_inputs(b, 1, h_q, s_kv, topk, seed=seed, device=device, data_on_device=True, model1=m1)
         valid = b * d["n_valid"]
-        return dict(kind="sparse_decode", inputs=d, s_q=1, b=b, h_q=h_q, tokens=valid,
-                    bytes=valid * 656 + b * h_q * D_QK * 2 + b * h_q * D_V * 2,
-                    flops=2.0 * h_q * valid * (D_QK + D_V),
-                    flops_padded=2.0 * h_q * b * topk * (D_QK + D_V),      # the reference's convention counts the -1 slots too
-                    desc=f"sparse fp8 MLA decode b={b} h_q={h_q} s_kv={s_kv} topk={topk} (5% padded -1) 656B records scale=amax/448")
+        return dict(kind="sparse_decode", inputs=d, s_q=1, b=b, h_q=h_q, tokens=valid, d_qk=d_qk,
+                    bytes=valid * rec + b * h_q * d_qk * 2 + b * h_q * D_V * 2,
+                    flops=2.0 * h_q * valid * (d_qk + D_V),
+                    flops_padded=2.0 * h_q * b * topk * (d_qk + D_V),      # the reference's convention counts the -1 slots too
+                    desc=f"sparse fp8 MLA decode b={b} h_q={h_q} s_kv={s_kv} topk={topk} (5% padded -1) " +
+                         ("584B records (d_qk 512) e8m0 scales" if m1 else "656B records scale=amax/448"))
     if name == "sparse_prefill":
         s_q, h_q, s_kv, topk = prefill_sq, 128, 32768, 2048
         d = W.sparse_prefill_inputs(s_q, h_q, s_kv, topk, causal_base=28672, seed=seed, device=device, data_on_device=True)
@@ -118,10 +122,12 @@ def config_of(w):
     return {"workload": w["desc"], "per_gpu_batch": w["b"], "l2": L2_NOTE}
 
 
-def run_step(w, sm_scale=D_QK ** -0.5):
+def run_step(w, sm_scale=None):
     """One pass through the public API on device-resident inputs."""
     import flashmla_b200 as fm
     d = w["inputs"]
+    if sm_scale is None:
+        sm_scale = w.get("d_qk", D_QK) ** -0.5
     if w["kind"] == "dense":
         out, lse = fm.flash_mla_with_kvcache(d["q"], d["blocked_k"], d["block_table"], d["cache_seqlens"], D_V, w["meta"], None, sm_scale, True)
     elif w["kind"] == "sparse_decode":
@@ -198,7 +204,7 @@ class E2EPipeline:
             out, lse = fm.flash_mla_with_kvcache(x["q"], d["blocked_k"], x["block_table"], x["cache_seqlens"], D_V, meta,
                                                  None, D_QK ** -0.5, True)
         elif w["kind"] == "sparse_decode":
-            out, lse = fm.flash_mla_with_kvcache(x["q"], d["kv_fp8"], None, None, D_V, w["meta"], None, D_QK ** -0.5,
+            out, lse = fm.flash_mla_with_kvcache(x["q"], d["kv_fp8"], None, None, D_V, w["meta"], None, w.get("d_qk", D_QK) ** -0.5,
                                                  False, True, x["indices"])
         else:
             out, _, lse = fm.flash_mla_sparse_fwd(x["q"], d["kv"], x["indices"], D_QK ** -0.5)
@@ -442,8 +448,8 @@ def cpu_baseline(w, budget_s=15.0, keep_outputs=False):
             idx_s = torch.where(idx >= 0, (remap[(idx.clamp_min(0) // 64).long()] * 64 + idx % 64).to(torch.int32), idx)
             qi = d["q"][i:i + 1].cpu()
             t0 = time.perf_counter()
-            kv_deq = quant.dequantize_v32(kv_raw)
-            o, l = attention.sparse_decode(qi, kv_deq, idx_s, D_QK ** -0.5, D_V)
+            kv_deq = quant.dequantize_model1(kv_raw) if w.get("d_qk") == 512 else quant.dequantize_v32(kv_raw)
+            o, l = attention.sparse_decode(qi, kv_deq, idx_s, w.get("d_qk", D_QK) ** -0.5, D_V)
             t_used += time.perf_counter() - t0
             if keep_outputs:
                 outs[i] = (o, l)
@@ -530,7 +536,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_prefill", "quantize"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_decode_m1", "sparse_prefill", "quantize"])
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--replays", type=int, default=0, help="passes per timed step (0: as many as make a step last about 20 ms)")

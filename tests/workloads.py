@@ -87,11 +87,12 @@ def dense_decode_inputs(cache_seqlens: torch.Tensor, s_q: int, h_q: int, h_kv: i
 
 def sparse_decode_inputs(b: int, s_q: int, h_q: int, s_kv: int, topk: int, pad_frac: float = 0.05, seed: int = 0,
                          device="cuda", pow2_scale: bool = False, pad_rows: int = 0,
-                         data_on_device: bool = False, page_size: int = BLOCK) -> Dict[str, torch.Tensor]:
+                         data_on_device: bool = False, page_size: int = BLOCK, model1: bool = False) -> Dict[str, torch.Tensor]:
     """FP8 cache of s_kv tokens per request (656-byte records, scale = amax/448) in pages of `page_size` tokens, random
     block table, indices = unique tokens drawn without replacement, the last pad_frac of each row set to -1,
-    expressed as physical positions page * page_size + offset."""
-    d = 576
+    expressed as physical positions page * page_size + offset.  model1: 512-wide queries and the 584-byte record form
+    (device data only)."""
+    d = 512 if model1 else 576
     blocks_per_seq = (s_kv + page_size - 1) // page_size
     num_blocks = b * blocks_per_seq
     g = _gen(seed + 1)
@@ -99,13 +100,22 @@ def sparse_decode_inputs(b: int, s_q: int, h_q: int, s_kv: int, topk: int, pad_f
     if data_on_device:
         gd = _gen(seed + 2, device)
         q = torch.randn(b, s_q, h_q, d, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
-        kv_fp8 = torch.empty(num_blocks, page_size + pad_rows, 656, dtype=torch.float8_e4m3fn, device=device)[:, :page_size].unsqueeze(2)
+        if model1:
+            from flashmla_b200.kvcache import model1_block_bytes, quantize_fp8_kvcache_model1
+            kv_fp8 = torch.zeros(num_blocks, model1_block_bytes(page_size), dtype=torch.uint8, device=device) \
+                .view(torch.float8_e4m3fn)[:, :page_size * 584].view(num_blocks, page_size, 1, 584)
+        else:
+            kv_fp8 = torch.empty(num_blocks, page_size + pad_rows, 656, dtype=torch.float8_e4m3fn, device=device)[:, :page_size].unsqueeze(2)
         step = max(1, 4096 * 64 // page_size)
         for i in range(0, num_blocks, step):
             n = min(step, num_blocks - i)
             chunk = torch.randn(n, page_size, 1, d, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
-            kv_fp8[i:i + n] = quantize_fp8_kvcache(chunk, pow2_scale)
+            if model1:
+                kv_fp8[i:i + n].view(torch.uint8).copy_(quantize_fp8_kvcache_model1(chunk).view(torch.uint8))
+            else:
+                kv_fp8[i:i + n] = quantize_fp8_kvcache(chunk, pow2_scale)
     else:
+        assert not model1, "the 512-wide form is generated on the device only"
         q = torch.randn(b, s_q, h_q, d, generator=g).to(torch.bfloat16)
         blocked_k = torch.randn(num_blocks, page_size, 1, d, generator=g).to(torch.bfloat16)
         kv_fp8 = quantize_fp8_kvcache(blocked_k, pow2_scale, pad_rows)
