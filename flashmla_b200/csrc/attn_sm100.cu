@@ -76,6 +76,9 @@ constexpr int NTHREADS_GATHER = 512;          // sparse modes: one more warpgrou
 constexpr long long WAIT_LIMIT_DEFAULT = 2000000000LL;    // SM cycles (about one second)
 constexpr long long DRAIN_LIMIT = 4000000LL;              // wind-down after an expired wait: per tracked operation
 constexpr long long SETTLE_CYCLES = 400000LL;             // ... and for copies between the two CTAs
+#ifndef MLA_TAIL_BULK
+#define MLA_TAIL_BULK 1
+#endif
 #ifndef MLA_SLEEP_NS
 #define MLA_SLEEP_NS 200u
 #endif
@@ -162,6 +165,7 @@ struct Params {
 // One unit of work of a partition: a request and the range of its 64-token blocks walked here.
 struct Work {
     int req, blk_begin, blk_end, ntiles, seqlen, is_split, slot;
+    int last;                   // dense decode: the partition's last request (nothing is loaded into the V ring after it)
     int len0, len1, nblk0;      // sparse decode: valid positions of the two index scopes, blocks of the first scope
 };
 
@@ -186,6 +190,7 @@ struct Walker<MODE_DENSE> {
         w.ntiles = (w.blk_end - w.blk_begin + 1) / 2;
         w.is_split = req == m.begin_req_idx ? m.is_first_req_splitted : (req == m.end_req_idx ? m.is_last_req_splitted : 0);
         w.slot = p.num_splits[req] + (req == m.begin_req_idx ? m.begin_split_idx : 0);
+        w.last = req == m.end_req_idx;
         return w;
     }
     __device__ void next() { ++req; }
@@ -1277,6 +1282,35 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             p.lse[w.req * p.l_sb + t * p.l_ss + hd * p.l_sh] = lse_nat;
                         }
                     }
+                } else if (DENSE && MLA_TAIL_BULK && w.last && has_tiles) {
+                    // The partition's last partial: the V ring is idle by now, so every thread stages its row there, half a
+                    // row (1 KiB) at a time, and hands it to the bulk-copy engine as one piece.  Stores by the thread itself
+                    // (one lane per row, 32 bytes per instruction) keep the load/store unit busy for 8 us per 256 KiB.
+                    const int64_t arow = ((int64_t)w.slot * p.s_q + t) * p.h_q + hd;
+                    float* orow = p.o_accum + arow * D_V;
+                    uint8_t* rowbuf = sm.data + VA_VRING + r * 1040;          // 1040: rows 16 bytes apart in the banks
+#pragma unroll 1
+                    for (int hf = 0; hf < 2; ++hf) {
+                        if (hf) bulk_wait_group_read0();
+#pragma unroll 1
+                        for (int c = 0; c < 8; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(tlane + hf * 256 + c * 32, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int k = 0; k < 8; ++k)
+                                *reinterpret_cast<uint4*>(rowbuf + c * 128 + k * 16) =
+                                    make_uint4(empty ? 0u : __float_as_uint(__uint_as_float(v[4 * k]) * scale),
+                                               empty ? 0u : __float_as_uint(__uint_as_float(v[4 * k + 1]) * scale),
+                                               empty ? 0u : __float_as_uint(__uint_as_float(v[4 * k + 2]) * scale),
+                                               empty ? 0u : __float_as_uint(__uint_as_float(v[4 * k + 3]) * scale));
+                        }
+                        fence_proxy_async_smem();
+                        if (row_ok) bulk_store_to_global(orow + hf * 256, smem_addr(rowbuf), 1024);
+                        bulk_commit_group();
+                    }
+                    if (row_ok) p.lse_accum[arow] = empty ? -INFINITY : log2f(Lsum) + M;
+                    bulk_wait_group0();
                 } else {
                     const int64_t arow = ((int64_t)w.slot * p.s_q + t) * p.h_q + hd;
                     float* orow = p.o_accum + arow * D_V;

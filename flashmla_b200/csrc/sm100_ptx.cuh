@@ -251,6 +251,15 @@ __device__ __forceinline__ uint4 ldg_evict_first(const uint4* p, uint64_t policy
 
 // Bulk copy from this CTA's shared memory into another CTA of the cluster; the bytes are counted on a
 // barrier of the destination CTA.  Addresses and size are multiples of 16 bytes.
+// Bulk store shared -> global (16-byte aligned addresses, size a multiple of 16), tracked by the thread's bulk groups
+__device__ __forceinline__ void bulk_store_to_global(void* dst, uint32_t src_local, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_local), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// this thread's bulk stores have read their shared-memory source / have completed
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_local, uint32_t bytes, uint32_t bar_cluster) {
     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_cluster), "r"(src_local), "r"(bytes), "r"(bar_cluster) : "memory");
