@@ -141,7 +141,6 @@ struct Params {
     int b, s_q, h_q, h_kv, g, rows, causal, num_blocks;
     int head_chunks;                       // dense mode: 64-column chunks between two kv heads of a cache row
     int max_blocks;                        // dense mode: width of the block table
-    int no_chunk8;                         // prefill with 512-wide rows: the ninth 64-column chunk of Q and K is all zeros
     float scale_log2;
     long long wait_limit;                  // SM cycles after which a barrier wait gives up
     const __nv_bfloat16* q; int64_t q_sb, q_ss, q_sh;
@@ -403,6 +402,8 @@ __device__ __noinline__ void load_q_by_threads(Smem& sm, const __nv_bfloat16* qr
 // ALT selects the second data format of a mode.  Dense mode: q, the cache and out are fp16 instead of bf16 (accumulation
 // is fp32 either way).  Sparse FP8 decode: the 512-wide record form (448 e4m3 + 64 bf16 RoPE per token, seven e8m0 scales
 // per token stored behind the block's tokens, V = all 512 dims): chunk 7 of a tile is the RoPE part, chunk 8 is zeros.
+// Sparse prefill: 512-wide rows; the ninth 64-column chunk of Q and K is zeros.  (A compile-time switch in every mode: the
+// same choice read from the parameters inside the gather loop cost the 576-wide prefill 8 %.)
 template <int MODE, bool ALT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == MODE_DENSE ? NTHREADS : NTHREADS_GATHER, 1)
 attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
@@ -413,6 +414,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     constexpr bool DENSE = MODE == MODE_DENSE;
     constexpr bool FP16 = ALT && MODE == MODE_DENSE;
     constexpr bool M1 = ALT && MODE == MODE_SPARSE_DECODE;
+    constexpr bool NO_CHUNK8 = ALT && MODE != MODE_DENSE;  // 512-wide rows
     constexpr int REC_BYTES = M1 ? 576 : 656;              // bytes between two tokens' values inside a block
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
@@ -947,9 +949,8 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                             const int rr = 4 * q4 + (lane >> 3);
                             const int rid = __shfl_sync(0xffffffffu, row_id, rr);
                             // (rows of 512 columns have no ninth chunk: zeros, as for an invalid token)
-                            const bool none = rid < 0 || p.no_chunk8;
-                            const __nv_bfloat16* src = none ? p.kv : p.kv + (int64_t)rid * p.kv_ss + (64 + c) * 8;
-                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, none ? 0u : 16u);
+                            const __nv_bfloat16* src = p.kv + (int64_t)(rid < 0 ? 0 : rid) * p.kv_ss + (NO_CHUNK8 ? 0 : (64 + c) * 8);
+                            cp_async16_zfill(dst0 + rr * 128 + ((c ^ (rr & 7)) << 4), src, (rid < 0 || NO_CHUNK8) ? 0u : 16u);
                         }
                     }
                     cp_async_arrive_noinc(smem_addr(&sm.kv_full[slot2]));
@@ -1074,7 +1075,7 @@ attn_sm100_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
                         tmem_wait_st();
                         if (!wt.aborted) mbar_arrive(smem_addr(&sm.ring_released));        // the producers may fill the ring with K now
                     } else {
-                        load_q_by_threads<MODE>(sm, qrow, row_ok, half, r, tlane, p.no_chunk8 != 0);
+                        load_q_by_threads<MODE>(sm, qrow, row_ok, half, r, tlane, NO_CHUNK8);
                     }
                     tmem_wait_st();
                     fence_proxy_async_smem();
@@ -1659,12 +1660,13 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     p.attn_sink = a.attn_sink;
     p.indices = a.indices; p.idx_ss = a.indices_stride_s; p.topk = a.topk; p.topk_len = a.topk_length; p.s_kv = a.s_kv;
     p.kv = (const __nv_bfloat16*)a.kv; p.kv_ss = a.kv_stride_s;
-    p.no_chunk8 = a.d_qk == 512 ? 1 : 0;
     p.status = a.status;
     p.row_blocks = (p.rows + ROWS - 1) / ROWS;
 
-    static bool configured[64] = {};
-    if (int rc = configure_once(attn_sm100_kernel<MODE_PREFILL, false>, configured)) return rc;
+    const bool d512 = a.d_qk == 512;
+    static bool configured[64] = {}, configured_512[64] = {};
+    if (int rc = d512 ? configure_once(attn_sm100_kernel<MODE_PREFILL, true>, configured_512)
+                      : configure_once(attn_sm100_kernel<MODE_PREFILL, false>, configured)) return rc;
     const int sms = current_device_num_sms();
     int pairs = sms / 2 / p.row_blocks;
     if (pairs < 1) pairs = 1;
@@ -1674,7 +1676,10 @@ int launch_sparse_prefill_sm100(const mla_sparse_prefill_args_t& a) {
     memset(&qmap, 0, sizeof(qmap));
     p.q_tma = encode_q_map(&qmap, a.q, 1, a.s_q, a.h_q, 0, a.q_stride_s, a.q_stride_h, a.h_q < ROWS ? a.h_q : ROWS, 1,
                            &p.q_box_bytes, false, a.d_qk) ? 1 : 0;
-    MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_PREFILL, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, kmap, kmap, qmap, p));
+    if (d512)
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_PREFILL, true>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, kmap, kmap, qmap, p));
+    else
+        MLA_CHECK_CUDA(launch_dependent(attn_sm100_kernel<MODE_PREFILL, false>, grid, dim3(NTHREADS_GATHER), sizeof(Smem), (cudaStream_t)a.stream, kmap, kmap, qmap, p));
     MLA_CHECK_CUDA(cudaGetLastError());
     return MLA_OK;
 }
@@ -1710,7 +1715,6 @@ int launch_sparse_decode_sm100(const mla_sparse_decode_args_t& a) {
     p.stopk[1] = a.extra_kv ? a.extra_topk : 0; p.stopk_len[1] = a.extra_topk_length;
 
     const bool m1 = a.d_qk == 512;                  // the 512-wide record form: the ninth chunk of Q and K is zeros
-    p.no_chunk8 = m1 ? 1 : 0;
     static bool configured[64] = {}, configured_m1[64] = {};
     if (int rc = m1 ? configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, true>, configured_m1)
                     : configure_once(attn_sm100_kernel<MODE_SPARSE_DECODE, false>, configured)) return rc;
