@@ -46,6 +46,17 @@ def shard_of_rank(n_total, world, rank):
     return rank * per, (rank + 1) * per
 
 
+def balanced_shard(seqlens, world, rank):
+    """Indices of the requests `rank` of `world` serves when the router balances KV tokens: requests sorted by length are
+    dealt to the ranks in serpentine order (0..world-1, world-1..0, ...), so every rank gets the same number of requests
+    and nearly the same number of tokens, whatever the length distribution."""
+    order = torch.argsort(seqlens.to(torch.int64), descending=True, stable=True)
+    pos = torch.arange(order.numel())
+    lap, k = pos // world, pos % world
+    owner = torch.where(lap % 2 == 0, k, world - 1 - k)
+    return torch.sort(order[owner == rank]).values
+
+
 def reduce_over_ranks(ms_total, ms_e2e_total, units, tokens, flops, nbytes, dist, device):
     """Whole-job figures from per-rank ones: times are the MAXIMUM over ranks (the job is as slow as its slowest
     rank), work is the SUM.  `dist` is torch.distributed (any backend) or None for a single process."""
@@ -84,15 +95,15 @@ def make_workload(name, device, seed, prefill_sq=4096):
         world = int(os.environ.get("WORLD_SIZE", "1"))
         rank = int(os.environ.get("RANK", "0"))
         seq_all = W.seqlens_lognormal(b_total, 8192, 1.0, 256, 131072, seed=0)
-        begin, end = shard_of_rank(b_total, world, rank)
-        per = end - begin
-        seq = seq_all[begin:end].contiguous()
+        mine = balanced_shard(seq_all, world, rank)
+        per = mine.numel()
+        seq = seq_all[mine].contiguous()
         d = W.dense_decode_inputs(seq, 1, h_q, 1, seed=seed, device=device, data_on_device=True)
         S = int(seq.sum())
         return dict(kind="dense", inputs=d, s_q=1, b=per, h_q=h_q, tokens=S,
                     bytes=S * D_QK * 2 + per * h_q * D_QK * 2 + per * h_q * D_V * 2,
                     flops=2.0 * h_q * S * (D_QK + D_V),
-                    desc=f"dense bf16 MLA decode b={b_total} total (batch-sharded) h_q=128 s_q=1 seqlens lognormal(median 8192, sigma 1) clip[256,131072]")
+                    desc=f"dense bf16 MLA decode b={b_total} total (batch-sharded, token-balanced) h_q=128 s_q=1 seqlens lognormal(median 8192, sigma 1) clip[256,131072]")
     if name in ("sparse_decode", "sparse_decode_m1"):
         # (_m1: the 512-wide "MODEL1" form - 584-byte records with e8m0 scales, d_qk = 512 - a side measurement)
         m1 = name == "sparse_decode_m1"

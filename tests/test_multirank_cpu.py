@@ -62,6 +62,21 @@ def test_single_process_reduction_is_identity():
     assert bench.shard_of_rank(1024, 8, 3) == (384, 512)
 
 
+def test_token_balanced_shards():
+    """The long-context sweep's router: disjoint shards of equal request count whose token sums differ by little."""
+    sys.path.insert(0, ROOT)
+    import bench
+    from tests import workloads as W
+    seq_all = W.seqlens_lognormal(1024, 8192, 1.0, 256, 131072, seed=0)
+    for world in (1, 2, 4, 8):
+        shards = [bench.balanced_shard(seq_all, world, r) for r in range(world)]
+        assert all(s.numel() == 1024 // world for s in shards)
+        assert torch.equal(torch.sort(torch.cat(shards)).values, torch.arange(1024))
+        tokens = torch.tensor([int(seq_all[s].sum()) for s in shards], dtype=torch.float64)
+        assert float(tokens.max() / tokens.mean()) < 1.02, tokens
+    # (contiguous slices of the same batch: the fullest rank is 8 % above the mean at 4 ranks, 18 % at 8)
+
+
 def test_reference_arm_is_rank0_only():
     """Under torchrun every rank starts `bench.py --impl reference`; all but rank 0 leave at once, silently."""
     env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
