@@ -16,8 +16,16 @@ Pinning status
   by importing those files unchanged; the vectors and the generating script
   live in tests/golden/.
 * tile-scheduler metadata: the reference holds no CPU implementation, no
-  golden vector and no test that pins metadata values, so the restatement in
-  sched_meta.py follows the CUDA source line by line and is pinned only by two
-  hand-derived known answers and by structural invariants -- "parity unpinned"
-  by the reference's own tests.
+  golden vector and no test that pins metadata values.  The restatement in
+  sched_meta.py is pinned against outputs of the reference itself: the
+  reference's own kernel
+  (csrc/smxx/decode/get_decoding_sched_meta/get_decoding_sched_meta.cu,
+  compiled unmodified into oracle/_ref/ by oracle/build_ref.py) runs beside it
+  in tests/test_gpu_sched_reference.py on the hand-derived known answers and on
+  about 270 random dense and sparse cases, value for value.  Where that library
+  has not been built, the known answers (tests/golden/
+  sched_meta_known_answers.json) and the schedule properties remain.
+* split-KV combine: the reference's own kernel (csrc/smxx/decode/combine/
+  combine.cu) is built into the same library and compared with this
+  repository's kernel in the same test file.
 """

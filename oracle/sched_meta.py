@@ -1,10 +1,12 @@
 """Tile-scheduler metadata: CPU restatement of
 csrc/smxx/decode/get_decoding_sched_meta/get_decoding_sched_meta.cu:11-107.
 
-TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).  Parity unpinned by the
-reference's tests: no golden vector exists upstream; the two known answers in
-tests/golden/sched_meta_known_answers.json were derived by hand from the CUDA
-source.
+TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).  No golden vector exists
+upstream; this restatement is pinned against the reference's own kernel, built
+unmodified by oracle/build_ref.py and run beside it in
+tests/test_gpu_sched_reference.py, and by the known answers in
+tests/golden/sched_meta_known_answers.json, which were derived by hand from the
+CUDA source (and which the reference kernel reproduces).
 
 Output layout (csrc/params.h:10-17): one row of 8 int32 per SM partition
   [begin_req_idx, end_req_idx (inclusive), begin_block_idx,

@@ -90,6 +90,24 @@ def test_model1_oracle_matches_reference(golden_dir):
         assert check_close("lse", lse, c["lse"], abs_tol=2e-6, rel_tol=1e-6)
 
 
+def test_sched_meta_oracle_matches_the_reference_kernel(golden_dir):
+    """tests/golden/sched_meta_reference.json holds what the reference's own CUDA kernel produced for 71 seeded dense and
+    sparse cases (tests/golden/make_sched_golden.py): the restatement has to reproduce every word."""
+    import json
+    cases = json.load(open(os.path.join(golden_dir, "sched_meta_reference.json")))["cases"]
+    assert len(cases) >= 70
+    for c in cases:
+        if "seqlens" in c:
+            meta, ns = sched_meta.get_sched_meta(len(c["seqlens"]), c["num_sm_parts"], c["block_size_n"], c["fixed_overhead"],
+                                                 seqlens_k=c["seqlens"])
+        else:
+            meta, ns = sched_meta.get_sched_meta(c["b"], c["num_sm_parts"], c["block_size_n"], c["fixed_overhead"], topk=c["topk"],
+                                                 extra_topk=c["extra_topk"], topk_length=c["topk_length"],
+                                                 extra_topk_length=c["extra_topk_length"])
+        assert np.asarray(meta)[:, :7].tolist() == c["meta"], c
+        assert np.asarray(ns).tolist() == c["num_splits"], c
+
+
 def test_uniform_costs_one_partition_per_request_never_split():
     """With equal request costs and as many partitions as requests the greedy scheduler cuts at every request boundary
     (the sparse decode path relies on this to skip the combine kernel)."""
