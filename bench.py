@@ -513,6 +513,58 @@ def metric_of(w):
     return "mla_dense_decode_hbm_gbs", "GB/s", w["bytes"] / 1e9
 
 
+def side_measurements(dev):
+    """The path's other workloads in short form (CUDA-graph replays of one pass: 3 steps of about 20 ms, then 3 cold-L2
+    passes), so that one default run carries a figure for every kernel of the path.  Parity of these workloads is the
+    job of the GPU tests and of `--workload <name>` runs, which check the timed result against the oracle."""
+    import flashmla_b200 as fm
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name in ("dense_sq2", "sparse_decode", "sparse_prefill"):
+        w = make_workload(name, dev, seed=0)
+        w["meta"] = fm.get_mla_metadata()[0]
+        for _ in range(3):
+            run_step(w)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            keep = run_step(w)
+        for _ in range(3):
+            graph.replay()
+        e0.record()
+        for _ in range(5):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        reps = max(1, min(400, int(round(TARGET_STEP_MS / max(e0.elapsed_time(e1) / 5, 1e-3)))))
+        total = 0.0
+        for _ in range(3):
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1) / reps
+        ms = total / 3
+        scrub = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+        cold = 0.0
+        for i in range(4):                         # the first pass only warms the scrub buffer's own mapping
+            scrub.fill_(1)
+            e0.record()
+            graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            if i:
+                cold += e0.elapsed_time(e1)
+        metric, unit, units = metric_of(w)
+        out[name] = {"metric": metric, "value": units / (ms / 1e3), "unit": unit, "ms_per_step": ms, "ms_per_step_cold_l2": cold / 3,
+                     "replays_per_step": reps, "tflops": w["flops"] / 1e12 / (ms / 1e3), "workload": w["desc"]}
+        if "flops_padded" in w:
+            out[name]["tflops_reference_convention"] = w["flops_padded"] / 1e12 / (ms / 1e3)
+        del graph, keep, scrub, w
+        torch.cuda.empty_cache()
+    return out
+
+
 def bench_quantize(args):
     """The cache-write kernel (bf16 token rows -> 656-byte FP8 records) on --quant-blocks (default 32768) blocks of 64 random rows: a side
     measurement of the step before sparse decode, one JSON line of its own."""
@@ -550,6 +602,7 @@ def main():
     ap.add_argument("--workload", default="dense", choices=["dense", "dense_sq2", "longctx", "sparse_decode", "sparse_decode_m1", "sparse_prefill", "quantize"])
     ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 portable kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="leave out the short measurements of the other workloads (default workload, one GPU)")
     ap.add_argument("--replays", type=int, default=0, help="passes per timed step (0: as many as make a step last about 20 ms)")
     ap.add_argument("--quant-blocks", type=int, default=32768, help="64-token blocks of the quantize workload (smaller for profiler captures)")
     ap.add_argument("--prefill-sq", type=int, default=4096, help="query tokens of the sparse_prefill workload (smaller for profiler captures)")
@@ -788,6 +841,15 @@ def main():
         # the result that was timed (the replayed graph's output) against the checker, unit by unit
         line["parity_checked"] = check_against_oracle(w, g_out, g_lse, r["outputs"])
         line["parity_bounds"] = {"out_cos_deficit": OUT_COS_TOL, "out_max_abs": OUT_ABS_TOL, "lse_abs": LSE_TOL}
+    # (not with a forced replay count: that is how profiler captures keep the run short)
+    if world == 1 and args.workload == "dense" and args.kernel == 0 and args.replays == 0 and not args.no_side:
+        del g_out, g_lse
+        w.clear()
+        torch.cuda.empty_cache()
+        try:
+            line["side_workloads"] = side_measurements(dev)
+        except Exception as exc:                  # a side measurement never takes the headline line with it
+            line["side_workloads"] = {"error": str(exc)}
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
